@@ -1,0 +1,113 @@
+"""Disentangled self-attention module with the fused sm_100a core.
+
+Same constructor, parameter names and ``forward`` signature as the reference's ``FlashDisentangledSelfAttention``
+(src/flashdeberta/model.py:97-252), which itself subclasses transformers' ``DisentangledSelfAttention``
+(models/deberta_v2/modeling_deberta_v2.py:137-184 for the parameters), so checkpoints and call sites carry over.
+What differs inside:
+
+* no ``q @ pos_key^T`` / ``k @ pos_query^T`` bias tensors (model.py:189-192, :210-214): the kernel takes the projected
+  position tables and contracts them per tile;
+* no pack / unpack per layer (model.py:216-231, :249): padded batches are handled in place from per-sequence lengths;
+* the mask may arrive as (B, L), as the (B, 1, L, L) tensor transformers' encoder builds, or as a (B,) int tensor of
+  lengths (what this package's encoder passes); right padding is assumed, as in the reference's varlen path.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfAttention
+
+from . import ops
+
+
+def lengths_from_mask(attention_mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """Per-sequence valid lengths (int32, on the mask's device) from any of the mask forms the module is handed.
+    Returns None for "everything valid".  No host synchronisation."""
+    if attention_mask is None:
+        return None
+    m = attention_mask
+    if m.dim() == 1:  # already lengths
+        return m.to(torch.int32)
+    if m.dim() == 4:  # (B, 1, L, L): row of the first token
+        m = m[:, 0, 0, :]
+    elif m.dim() == 3:  # (B, L, L)
+        m = m[:, 0, :]
+    elif m.dim() != 2:
+        raise ValueError(f"attention_mask with {attention_mask.dim()} dims is not supported")
+    return (m != 0).sum(dim=-1, dtype=torch.int32)
+
+
+class FlashDisentangledSelfAttention(DisentangledSelfAttention):
+    """Drop-in for src/flashdeberta/model.py:97 of the reference."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._pos_cache = None
+
+    # -- position tables ------------------------------------------------------------------------------------------------
+    def _heads_first(self, x: torch.Tensor) -> torch.Tensor:
+        # (rows, H*D) -> (H, rows, D)
+        return x.view(x.shape[0], self.num_attention_heads, -1).permute(1, 0, 2).contiguous()
+
+    def _position_tables(self, rel_embeddings: torch.Tensor, dtype: torch.dtype):
+        """pos_key_layer / pos_query_layer of model.py:159-177, head-major (H, 2*span, D).  They do not depend on the
+        input, so in eval mode they are kept until a parameter or the embedding table changes."""
+        c2p = "c2p" in self.pos_att_type
+        p2c = "p2c" in self.pos_att_type
+        if self.share_att_key:
+            wk, wq = self.key_proj, self.query_proj
+        else:
+            wk, wq = getattr(self, "pos_key_proj", None), getattr(self, "pos_query_proj", None)
+        key = None
+        if not self.training and not torch.is_grad_enabled():
+            key = (id(rel_embeddings), rel_embeddings._version, rel_embeddings.device, dtype,
+                   tuple((p.data_ptr(), p._version) for m in (wk, wq) if m is not None for p in m.parameters()))
+            if self._pos_cache is not None and self._pos_cache[0] == key:
+                return self._pos_cache[1], self._pos_cache[2]
+        span2 = 2 * self.pos_ebd_size
+        rel = self.pos_dropout(rel_embeddings)[:span2]
+        pos_key = self._heads_first(wk(rel)).to(dtype) if c2p else None
+        pos_query = self._heads_first(wq(rel)).to(dtype) if p2c else None
+        if key is not None:
+            self._pos_cache = (key, pos_key, pos_query, rel_embeddings)  # keep the table alive so id() stays unique
+        return pos_key, pos_query
+
+    # -- forward -------------------------------------------------------------------------------------------------------------
+    def forward(self, hidden_states, attention_mask, output_attentions=False, query_states=None, relative_pos=None,
+                rel_embeddings=None):
+        """Returns ``(context (B, L, hidden), None)`` like model.py:252.  ``relative_pos`` is ignored, as in the
+        reference (model.py:105): positions are always 0..len-1 inside each sequence.  Padded rows come back zero."""
+        if output_attentions:
+            raise ValueError("the fused attention never materialises attention probabilities; "
+                             "use the eager implementation for output_attentions=True")
+        if query_states is None:
+            query_states = hidden_states
+        B, L, _ = hidden_states.shape
+        H, D = self.num_attention_heads, self.attention_head_size
+        in_dtype = hidden_states.dtype
+
+        q = self.query_proj(query_states).view(B, L, H, D)
+        k = self.key_proj(hidden_states).view(B, L, H, D)
+        v = self.value_proj(hidden_states).view(B, L, H, D)
+
+        scale_factor = 1 + int("c2p" in self.pos_att_type) + int("p2c" in self.pos_att_type)
+        sm_scale = 1.0 / math.sqrt(D * scale_factor)
+
+        pos_key = pos_query = None
+        buckets, max_rel = -1, -1
+        if self.relative_attention and scale_factor > 1:
+            if rel_embeddings is None:
+                raise ValueError("rel_embeddings is required when relative_attention is on")
+            pos_key, pos_query = self._position_tables(rel_embeddings, torch.bfloat16)
+            buckets, max_rel = self.position_buckets, self.max_relative_positions
+
+        if in_dtype != torch.bfloat16:
+            q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        seq_lens = lengths_from_mask(attention_mask)
+        out = ops.attn_fwd_op(q, k, v, pos_key, pos_query, None, seq_lens, L, sm_scale, buckets, max_rel)
+        out = out.view(B, L, H * D)
+        if in_dtype != torch.bfloat16:
+            out = out.to(in_dtype)
+        return (out, None)

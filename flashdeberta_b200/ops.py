@@ -1,0 +1,278 @@
+"""Op layer: torch tensors in, one call into libfdb_b200.so, torch tensor out.
+
+Takes the place of the reference's Triton op module (src/flashdeberta/ops/flash_attention.py:1088-1091 and
+src/flashdeberta/ops/flash_attention_varlen.py:485-511).  The signature differs on purpose: the reference's ops take the
+two pre-multiplied bias tensors ``q @ pos_key^T`` and ``k @ pos_query^T`` (model.py:189-192); these take the projected
+position tables themselves and the products never exist in global memory.
+
+Forward only, like the reference's packed op (flash_attention_varlen.py:481-483 raises in backward).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib, bucket
+
+__all__ = [
+    "disentangled_attention", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3",
+    "check_status", "launch_count",
+]
+
+_status: Dict[str, torch.Tensor] = {}
+_launches = 0  # kernels this module asked the library to launch (the benchmark reports it)
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device=None) -> None:
+    """Read the device status word (synchronises) and raise if a kernel reported an anomaly."""
+    for key, t in list(_status.items()):
+        if device is not None and key != str(torch.device(device)):
+            continue
+        v = int(t.item())
+        if v:
+            t.zero_()
+            what = []
+            if v & _lib.FDB_DEV_TIMEOUT:
+                what.append("a bounded wait inside the attention kernel ran out (output invalid)")
+            if v & _lib.FDB_DEV_BAD_SEQLEN:
+                what.append("cu_seqlens/seq_lens hold a length below zero or above max_seqlen")
+            raise RuntimeError("flashdeberta_b200 device status %d: %s" % (v, "; ".join(what)))
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _lib.FDB_BF16
+    if t.dtype == torch.float32:
+        return _lib.FDB_FP32
+    if t.dtype == torch.float8_e4m3fn:
+        return _lib.FDB_E4M3
+    raise TypeError(f"unsupported dtype {t.dtype}")
+
+
+def _rows_view(x: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
+    """(rows, H, D) view of a (rows, H, D) or (B, L, H, D) tensor without copying when the layout allows it.
+    Returns the view, its row stride and head stride in elements."""
+    if x.dim() == 4:
+        B, L, H, D = x.shape
+        if x.stride(0) != L * x.stride(1):
+            x = x.contiguous()
+        x = x.as_strided((B * L, H, D), (x.stride(1), x.stride(2), x.stride(3)), x.storage_offset())
+    if x.dim() != 3:
+        raise ValueError("expected (rows, heads, head_dim) or (batch, seq, heads, head_dim)")
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    return x, x.stride(0), x.stride(1)
+
+
+def _fill_params(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
+                 max_relative_positions, out, lse, scales=None):
+    dev = q.device
+    q3, q_rs, q_hs = _rows_view(q)
+    k3, k_rs, k_hs = _rows_view(k)
+    v3, v_rs, v_hs = _rows_view(v)
+    rows, H, D = q3.shape
+    if k3.shape != q3.shape or v3.shape != q3.shape:
+        raise ValueError("q, k and v must have the same shape")
+    p = _lib.AttnParams()
+    p.struct_bytes = C.sizeof(_lib.AttnParams)
+    p.dtype = _dtype_code(q3)
+    keep = [q3, k3, v3]
+    p.q, p.k, p.v, p.out = q3.data_ptr(), k3.data_ptr(), v3.data_ptr(), out.data_ptr()
+    p.q_row_stride, p.q_head_stride = q_rs, q_hs
+    p.k_row_stride, p.k_head_stride = k_rs, k_hs
+    p.v_row_stride, p.v_head_stride = v_rs, v_hs
+    p.out_row_stride, p.out_head_stride = H * D, D
+    span = bucket.att_span(position_buckets, max_relative_positions)
+    for name, t in (("pos_key", pos_key), ("pos_query", pos_query)):
+        if t is None:
+            continue
+        if t.dim() == 4 and t.shape[0] == 1:
+            t = t[0]
+        if t.shape != (H, 2 * span, D):
+            raise ValueError(f"{name} must be (heads, 2*att_span, head_dim) = {(H, 2 * span, D)}, got {tuple(t.shape)}")
+        if t.dtype != q3.dtype:
+            raise TypeError(f"{name} dtype {t.dtype} differs from q dtype {q3.dtype}")
+        t = t.contiguous()
+        keep.append(t)
+        setattr(p, name, t.data_ptr())
+    if pos_key is not None or pos_query is not None:
+        lut, d_min = bucket.device_lut(position_buckets, max_relative_positions, dev)
+        p.bucket_lut, p.lut_d_min, p.lut_len = lut.data_ptr(), d_min, lut.numel()
+    if cu_seqlens is not None:
+        if cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_contiguous():
+            cu_seqlens = cu_seqlens.to(torch.int32).contiguous()
+        keep.append(cu_seqlens)
+        p.cu_seqlens = cu_seqlens.data_ptr()
+        p.batch = cu_seqlens.numel() - 1
+    else:
+        if q.dim() != 4:
+            raise ValueError("dense layout needs (batch, seq, heads, head_dim) inputs")
+        p.batch = q.shape[0]
+        if max_seqlen != q.shape[1]:
+            raise ValueError("dense layout: max_seqlen must equal the padded length")
+        if seq_lens is not None:
+            if seq_lens.dtype != torch.int32 or not seq_lens.is_contiguous():
+                seq_lens = seq_lens.to(torch.int32).contiguous()
+            keep.append(seq_lens)
+            p.seq_lens = seq_lens.data_ptr()
+    p.max_seqlen, p.total_rows, p.heads, p.head_dim = int(max_seqlen), rows, H, D
+    p.position_buckets, p.max_relative_positions = int(position_buckets), int(max_relative_positions)
+    p.sm_scale = float(sm_scale)
+    if scales is not None:
+        for name, t in scales.items():
+            if t is not None:
+                t = t.to(torch.float32).contiguous()
+                keep.append(t)
+                setattr(p, name, t.data_ptr())
+    if lse is not None:
+        p.lse = lse.data_ptr()
+    p.status = _status_word(dev).data_ptr()
+    return p, keep
+
+
+def _out_like(q: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    return torch.empty(q.shape, dtype=dtype, device=q.device)
+
+
+def disentangled_attention(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    pos_key: Optional[torch.Tensor], pos_query: Optional[torch.Tensor],
+    *, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
+    max_seqlen: int, sm_scale: Optional[float] = None, position_buckets: int = -1, max_relative_positions: int = -1,
+    return_lse: bool = False, scales: Optional[dict] = None,
+):
+    """softmax((Q K^T + c2p + p2c) * sm_scale) V on the fused sm_100a kernel.
+
+    q, k, v: (B, L, H, 64) [dense, right-padded, lengths in ``seq_lens`` or all L] or (T, H, 64) [packed, with
+    ``cu_seqlens``]; bf16 (or float8_e4m3fn with ``scales``).  pos_key / pos_query: (H, 2*att_span, 64) projected
+    relative-position tables or None.  Returns bf16 of q's shape (and the natural-log LSE (rows, H) when asked).
+    """
+    global _launches
+    if not q.is_cuda:
+        raise RuntimeError("flashdeberta_b200 runs on CUDA devices only; there is no CPU path")
+    lib = _lib.load()
+    D = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D * (1 + int(pos_key is not None) + int(pos_query is not None)))
+    out = _out_like(q, torch.bfloat16)
+    rows = out.numel() // (out.shape[-1] * out.shape[-2])
+    lse = torch.empty(rows, q.shape[-2], dtype=torch.float32, device=q.device) if return_lse else None
+    with torch.cuda.device(q.device):
+        p, keep = _fill_params(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale,
+                               position_buckets, max_relative_positions, out, lse, scales)
+        need = lib.fdb_attn_workspace_bytes(C.byref(p))
+        if need == 0:  # invalid parameters (raises with the library's message) or an empty batch
+            _lib.check(lib.fdb_attn_fwd(C.byref(p), None))
+            return (out, lse) if return_lse else out
+        ws = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
+        base = (ws.data_ptr() + 255) & ~255
+        p.workspace, p.workspace_bytes = base, need
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        _lib.check(lib.fdb_attn_fwd(C.byref(p), C.c_void_p(stream)))
+        _launches += 2 + int(pos_key is not None or pos_query is not None)
+        # `keep` and `ws` were allocated on this stream, so the caching allocator reuses them in stream order
+        del keep, ws
+    return (out, lse) if return_lse else out
+
+
+def disentangled_attention_check(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    pos_key: Optional[torch.Tensor], pos_query: Optional[torch.Tensor],
+    *, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
+    max_seqlen: int, sm_scale: Optional[float] = None, position_buckets: int = -1, max_relative_positions: int = -1,
+    return_lse: bool = False,
+):
+    """Same contract on the library's plain-fp32 check kernel (bf16 or fp32 inputs, head_dim <= 128).  Validation only."""
+    global _launches
+    if not q.is_cuda:
+        raise RuntimeError("flashdeberta_b200 runs on CUDA devices only; there is no CPU path")
+    lib = _lib.load()
+    D = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D * (1 + int(pos_key is not None) + int(pos_query is not None)))
+    out = _out_like(q, q.dtype)
+    rows = out.numel() // (out.shape[-1] * out.shape[-2])
+    lse = torch.empty(rows, q.shape[-2], dtype=torch.float32, device=q.device) if return_lse else None
+    with torch.cuda.device(q.device):
+        p, keep = _fill_params(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale,
+                               position_buckets, max_relative_positions, out, lse)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        _lib.check(lib.fdb_attn_fwd_check(C.byref(p), C.c_void_p(stream)))
+        _launches += 1
+    return (out, lse) if return_lse else out
+
+
+def relative_index_matrix(len_q: int, len_k: int, position_buckets: int, max_relative_positions: int,
+                          device) -> torch.Tensor:
+    """(len_q, len_k) int32 matrix of position-table rows as the device code looks them up (for the bit-exactness test
+    against transformers' build_relative_position + clamp)."""
+    global _launches
+    lib = _lib.load()
+    device = torch.device(device)
+    lut, d_min = bucket.device_lut(position_buckets, max_relative_positions, device)
+    out = torch.empty(len_q, len_k, dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        stream = torch.cuda.current_stream(device).cuda_stream
+        _lib.check(lib.fdb_relative_index_matrix(lut.data_ptr(), d_min, lut.numel(), len_q, len_k, out.data_ptr(),
+                                                 C.c_void_p(stream)))
+        _launches += 1
+    return out
+
+
+def quantize_e4m3(x: torch.Tensor, slab_start: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 (rows, H, D) -> (float8_e4m3fn (rows, H, D) contiguous, scale (n_slabs, H) fp32) with one amax-derived scale per
+    (slab, head); slab s = rows [slab_start[s], slab_start[s+1])."""
+    global _launches
+    lib = _lib.load()
+    x3, rs, hs = _rows_view(x)
+    rows, H, D = x3.shape
+    slab_start = slab_start.to(torch.int32).contiguous()
+    n = slab_start.numel() - 1
+    y = torch.empty(rows, H, D, dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty(n, H, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(lib.fdb_quantize_e4m3(x3.data_ptr(), rs, hs, slab_start.data_ptr(), n, H, D, y.data_ptr(),
+                                         scale.data_ptr(), C.c_void_p(stream)))
+        _launches += 1
+    return y.view(x.shape), scale
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# torch custom op (so the call shows up as one node for tracing / meta tensors); thin wrapper over the function above
+# --------------------------------------------------------------------------------------------------------------------
+@torch.library.custom_op("flashdeberta_b200::attn_fwd", mutates_args=())
+def attn_fwd_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: Optional[torch.Tensor],
+                pos_query: Optional[torch.Tensor], cu_seqlens: Optional[torch.Tensor],
+                seq_lens: Optional[torch.Tensor], max_seqlen: int, sm_scale: float, position_buckets: int,
+                max_relative_positions: int) -> torch.Tensor:
+    return disentangled_attention(q, k, v, pos_key, pos_query, cu_seqlens=cu_seqlens, seq_lens=seq_lens,
+                                  max_seqlen=max_seqlen, sm_scale=sm_scale, position_buckets=position_buckets,
+                                  max_relative_positions=max_relative_positions)
+
+
+@attn_fwd_op.register_fake
+def _(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
+      max_relative_positions):
+    return torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
+
+
+def _no_backward(ctx, grad):
+    raise RuntimeError("flashdeberta_b200::attn_fwd is forward-only (inference); no backward is implemented")
+
+
+attn_fwd_op.register_autograd(_no_backward)

@@ -1,0 +1,183 @@
+/*
+ * fdb_b200.h — C ABI of libfdb_b200.so: DeBERTa-v2/v3 disentangled self-attention forward for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes; no libtorch type crosses this boundary.  The caller
+ * owns every buffer (inputs, outputs, workspace, status word); the library allocates no device memory
+ * unless an entry point's comment says otherwise.  Functions return 0 (FDB_OK) or a negative fdb_status
+ * code; fdb_last_error() gives the text of the calling thread's last failure.  Nothing is launched when
+ * an argument check fails.
+ *
+ * The "reference" cited below is Knowledgator/FlashDeBERTa 0.0.5 (paths relative to its root) and, where
+ * marked HF, transformers' models/deberta_v2/modeling_deberta_v2.py, which the reference subclasses.
+ */
+#ifndef FDB_B200_H_
+#define FDB_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDB_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define FDB_API __attribute__((visibility("default")))
+#else
+#define FDB_API
+#endif
+
+typedef enum fdb_status {
+  FDB_OK = 0,
+  FDB_ERR_INVALID_ARGUMENT = -1, /* NULL where a pointer is required, bad size, bad enum */
+  FDB_ERR_UNSUPPORTED = -2,      /* valid in the reference, not built here (e.g. head_dim != 64 in the fused kernel) */
+  FDB_ERR_ALIGNMENT = -3,        /* pointer or stride not 16-byte aligned */
+  FDB_ERR_WORKSPACE = -4,        /* workspace missing or too small */
+  FDB_ERR_CUDA = -5,             /* a CUDA runtime/driver call failed; see fdb_last_error() */
+  FDB_ERR_LIMIT = -6             /* size above a stated fixed maximum */
+} fdb_status;
+
+typedef enum fdb_dtype {
+  FDB_BF16 = 0,
+  FDB_FP32 = 1, /* check kernel only */
+  FDB_E4M3 = 2  /* fused kernel, per-head scales */
+} fdb_dtype;
+
+/* Bits of the device status word written by kernels (0 = no anomaly). */
+#define FDB_DEV_TIMEOUT 1u      /* a bounded wait inside a kernel ran out; the output is invalid */
+#define FDB_DEV_BAD_SEQLEN 2u   /* cu_seqlens not monotone / a length below zero or above max_seqlen */
+
+/*
+ * One attention call.  Replaces, in one launch sequence, what the reference does in
+ *   src/flashdeberta/model.py:185-204 (fixed length) and :206-249 (packed),
+ *   src/flashdeberta/ops/flash_attention.py:1088-1091 -> :421-488 -> kernel :146-300,
+ *   src/flashdeberta/ops/flash_attention_varlen.py:485-511 -> :349-440 -> kernel :85-225,
+ * including the two bias GEMMs (model.py:189-192, :210-214) that the reference leaves to cuBLAS.
+ *
+ * Tensors are addressed as element (row, head, d) = base + row*row_stride + head*head_stride + d, strides in
+ * ELEMENTS, d contiguous.  "row" counts tokens over the whole batch:
+ *   dense  (cu_seqlens == NULL): sequence b owns rows [b*max_seqlen, b*max_seqlen + len_b),
+ *                                len_b = seq_lens ? seq_lens[b] : max_seqlen   (right padding)
+ *   packed (cu_seqlens != NULL): sequence b owns rows [cu_seqlens[b], cu_seqlens[b+1]).
+ * Output rows that belong to no sequence (dense padding) are written as zeros, as
+ * src/flashdeberta/padding.py:30-44 does.  Padding rows of v must hold finite numbers.
+ */
+typedef struct fdb_attn_params {
+  uint32_t struct_bytes; /* sizeof(fdb_attn_params), checked */
+  int32_t dtype;         /* fdb_dtype of q, k, v, pos_key, pos_query; out is bf16 (fp32 for FDB_FP32) */
+
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  int64_t q_row_stride, q_head_stride;
+  int64_t k_row_stride, k_head_stride;
+  int64_t v_row_stride, v_head_stride;
+  int64_t out_row_stride, out_head_stride;
+
+  /* Projected relative-position tables, (heads, 2*att_span, head_dim) contiguous, i.e. pos_key_layer and
+   * pos_query_layer of model.py:159-177 in head-major order.  NULL switches the term off
+   * (c2p needs pos_key, p2c needs pos_query). */
+  const void* pos_key;
+  const void* pos_query;
+
+  const int32_t* cu_seqlens; /* device, batch+1 entries, or NULL */
+  const int32_t* seq_lens;   /* device, batch entries, or NULL (dense only) */
+
+  int32_t batch;
+  int32_t max_seqlen; /* dense: padded length L.  packed: an upper bound on every length */
+  int32_t total_rows; /* number of rows addressable in q/k/v/out (dense: batch*max_seqlen) */
+  int32_t heads;
+  int32_t head_dim;
+
+  /* position_buckets / max_relative_positions as in HF:168-174; att_span = buckets > 0 ? buckets : max_rel */
+  int32_t position_buckets;
+  int32_t max_relative_positions;
+
+  /* Device copy of the table made by fdb_build_bucket_lut (int16, lut_len entries); entry i is the table row for
+   * relative distance d = lut_d_min + i; distances outside use the first / last entry. */
+  const int16_t* bucket_lut;
+  int32_t lut_d_min;
+  int32_t lut_len;
+
+  float sm_scale; /* 1/sqrt(head_dim * (1 + [c2p] + [p2c])), model.py:151-157 */
+
+  /* FDB_E4M3 only: device float arrays, value = stored * scale.  q/k/v scales have batch*heads entries
+   * (sequence-major), table scales have `heads` entries. */
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  const float* pos_key_scale;
+  const float* pos_query_scale;
+
+  float* lse; /* optional, (total_rows, heads) fp32 natural-log LSE as flash_attention.py:293 */
+
+  void* workspace; /* device, >= fdb_attn_workspace_bytes(), 256-byte aligned */
+  uint64_t workspace_bytes;
+
+  int32_t* status; /* device int32, OR-ed with FDB_DEV_* bits; may be NULL */
+} fdb_attn_params;
+
+/* Library / ABI version (FDB_ABI_VERSION the library was built with). */
+FDB_API int fdb_abi_version(void);
+
+/* Text of the calling thread's most recent error ("" if none). */
+FDB_API const char* fdb_last_error(void);
+
+/* Text for an fdb_status code. */
+FDB_API const char* fdb_status_string(int code);
+
+/*
+ * Host-side integer table for the log-bucket relative index: replaces the per-score-element float math at
+ * src/flashdeberta/ops/flash_attention.py:236-254 and HF:56-69 + the clamp at HF:318/:336.
+ * Writes into out[0..*len) the table row for every distance d in [*d_min, *d_min + *len); the first and last
+ * entries are the saturated values that hold for every distance beyond.  Pass out == NULL to query *len and
+ * *d_min only.  capacity = entries available in out.
+ */
+FDB_API int fdb_build_bucket_lut(int32_t position_buckets, int32_t max_relative_positions, int16_t* out, int32_t capacity,
+                         int32_t* d_min, int32_t* len);
+
+/* Single distance -> table row, same arithmetic as fdb_build_bucket_lut (host). */
+FDB_API int32_t fdb_relative_index(int32_t position_buckets, int32_t max_relative_positions, int64_t distance);
+
+/* Bytes of device workspace fdb_attn_fwd needs for these parameters (0 on invalid parameters, see fdb_last_error). */
+FDB_API uint64_t fdb_attn_workspace_bytes(const fdb_attn_params* p);
+
+/*
+ * Fused forward: tcgen05/TMEM tensor-core kernel fed by TMA.  bf16 or e4m3 inputs, head_dim 64.
+ * Launches on `stream` (a cudaStream_t passed as void*); returns without synchronising.
+ * Replaces flash_attention_with_disentangled (flash_attention.py:1088) and its varlen twin
+ * (flash_attention_varlen.py:485), plus model.py:189-192/:210-214.
+ */
+FDB_API int fdb_attn_fwd(const fdb_attn_params* p, void* stream);
+
+/*
+ * Check kernel: the same contract computed with fp32 arithmetic on CUDA cores, one warp per (row, head), no
+ * tensor cores, bucket index looked up per element from bucket_lut.  bf16 or fp32 inputs, head_dim <= 128.
+ * Needs no workspace.  For validation, never for speed.
+ */
+FDB_API int fdb_attn_fwd_check(const fdb_attn_params* p, void* stream);
+
+/*
+ * Device dump of the relative index the kernels use: out[m*len_k + n] = row for distance (m - n), m < len_q,
+ * n < len_k, via the same device lookup as the attention kernels.  For the bit-exactness test against
+ * HF:72-101 + :318.
+ */
+FDB_API int fdb_relative_index_matrix(const int16_t* bucket_lut, int32_t lut_d_min, int32_t lut_len, int32_t len_q,
+                              int32_t len_k, int32_t* out, void* stream);
+
+/*
+ * Per-slab amax scaling to e4m3 (no counterpart in the reference; the FP8 option of this library).
+ * x is (rows, heads, head_dim) strided like q; slab s covers rows [slab_start[s], slab_start[s+1]) of one head
+ * (slab_start device int32, n_slabs+1 entries; pass the cu_seqlens array).  Writes y (e4m3, contiguous
+ * (rows, heads, head_dim)) and scale[s*heads + h] = amax/448.
+ */
+FDB_API int fdb_quantize_e4m3(const void* x_bf16, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
+                      int32_t n_slabs, int32_t heads, int32_t head_dim, void* y_e4m3, float* scale, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDB_B200_H_ */
