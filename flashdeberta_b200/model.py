@@ -1,0 +1,170 @@
+"""DeBERTa-v2/v3 backbone and task heads with the fused attention core.
+
+Thin subclasses of transformers' DeBERTa-v2 classes, exposing the names the reference exports
+(src/flashdeberta/__init__.py:1-9; classes at src/flashdeberta/model.py:259-920).  Parameter names and shapes are
+those of transformers, so stock checkpoints load unchanged.  Differences from the reference's wrappers:
+
+* the encoder hands every layer the per-sequence lengths (B,) instead of a (B, 1, L, L) mask and never builds the
+  (1, L, L) int64 relative-position matrix the flash path ignores (the reference inherits both from
+  transformers' encoder forward, src/flashdeberta/model.py:275-310);
+* ``config.attn_backend`` chooses the attention core: ``"b200"`` (default, fused kernel) or ``"eager"``
+  (transformers' own module).  The reference keys the same switch on ``config._attn_implementation``
+  (model.py:254-262), which transformers 5 reserves for its own back-ends.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+from transformers.modeling_outputs import BaseModelOutput
+from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+from transformers.models.deberta_v2.modeling_deberta_v2 import (
+    DebertaV2Attention,
+    DebertaV2Encoder,
+    DebertaV2ForMaskedLM,
+    DebertaV2ForMultipleChoice,
+    DebertaV2ForQuestionAnswering,
+    DebertaV2ForSequenceClassification,
+    DebertaV2ForTokenClassification,
+    DebertaV2Layer,
+    DebertaV2Model,
+    DebertaV2PreTrainedModel,
+    DisentangledSelfAttention,
+)
+
+from .attention import FlashDisentangledSelfAttention, lengths_from_mask
+
+__all__ = [
+    "DEBERTA_SELF_ATTENTION_CLASSES", "FlashDebertaV2Attention", "FlashDebertaV2Layer", "FlashDebertaV2Encoder",
+    "FlashDebertaV2PreTrainedModel", "FlashDebertaV2Model", "FlashDebertaV2ForMaskedLM",
+    "FlashDebertaV2ForSequenceClassification", "FlashDebertaV2ForTokenClassification",
+    "FlashDebertaV2ForQuestionAnswering", "FlashDebertaV2ForMultipleChoice",
+]
+
+# same role as DEBERTA_SELF_ATTENTION_CLASSES at src/flashdeberta/model.py:254-257
+DEBERTA_SELF_ATTENTION_CLASSES = {
+    "eager": DisentangledSelfAttention,
+    "b200": FlashDisentangledSelfAttention,
+    "flash_attention_2": FlashDisentangledSelfAttention,  # the reference's name for its flash path
+}
+
+
+def _backend(config) -> str:
+    name = getattr(config, "attn_backend", "b200")
+    if name not in DEBERTA_SELF_ATTENTION_CLASSES:
+        raise ValueError(f"config.attn_backend must be one of {sorted(DEBERTA_SELF_ATTENTION_CLASSES)}, got {name!r}")
+    return name
+
+
+class FlashDebertaV2Attention(DebertaV2Attention):
+    def __init__(self, config):
+        super().__init__(config)
+        self.self = DEBERTA_SELF_ATTENTION_CLASSES[_backend(config)](config)
+
+
+class FlashDebertaV2Layer(DebertaV2Layer):
+    def __init__(self, config):
+        super().__init__(config)
+        self.attention = FlashDebertaV2Attention(config)
+
+
+class FlashDebertaV2Encoder(DebertaV2Encoder):
+    def __init__(self, config):
+        super().__init__(config)
+        self.layer = nn.ModuleList([FlashDebertaV2Layer(config) for _ in range(config.num_hidden_layers)])
+        self._fused = _backend(config) != "eager"
+        self._rel_cache = None
+
+    def get_rel_embedding(self):
+        """LayerNorm(rel_embeddings) does not depend on the input: in eval mode it is computed once and reused, which
+        also lets every layer keep its projected position tables."""
+        if self.training or torch.is_grad_enabled() or not self.relative_attention:
+            return super().get_rel_embedding()
+        w = self.rel_embeddings.weight
+        key = [w.data_ptr(), w._version, w.dtype, w.device]
+        if "layer_norm" in self.norm_rel_ebd:
+            key += [self.LayerNorm.weight._version, self.LayerNorm.bias._version, self.LayerNorm.weight.data_ptr()]
+        if self._rel_cache is None or self._rel_cache[0] != key:
+            self._rel_cache = (key, super().get_rel_embedding())
+        return self._rel_cache[1]
+
+    def forward(self, hidden_states, attention_mask, output_hidden_states=True, output_attentions=False,
+                query_states=None, relative_pos=None, return_dict=True):
+        if not self._fused:
+            return super().forward(hidden_states, attention_mask, output_hidden_states, output_attentions,
+                                   query_states, relative_pos, return_dict)
+        if attention_mask.dim() <= 2:
+            input_mask = attention_mask
+        else:
+            input_mask = attention_mask.sum(-2) > 0
+        seq_lens = lengths_from_mask(attention_mask)  # (B,) int32; the only form of the mask the layers see
+
+        all_hidden_states = (hidden_states,) if output_hidden_states else None
+        next_kv = hidden_states
+        rel_embeddings = self.get_rel_embedding()
+        output_states = hidden_states
+        for i, layer_module in enumerate(self.layer):
+            output_states, _ = layer_module(next_kv, seq_lens, query_states=query_states, relative_pos=None,
+                                            rel_embeddings=rel_embeddings, output_attentions=output_attentions)
+            if i == 0 and self.conv is not None:
+                output_states = self.conv(hidden_states, output_states, input_mask)
+            if output_hidden_states:
+                all_hidden_states = all_hidden_states + (output_states,)
+            if query_states is not None:
+                query_states = output_states
+                if isinstance(hidden_states, (list, tuple)):
+                    next_kv = hidden_states[i + 1] if i + 1 < len(self.layer) else None
+            else:
+                next_kv = output_states
+        if not return_dict:
+            return tuple(v for v in [output_states, all_hidden_states, None] if v is not None)
+        return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden_states, attentions=None)
+
+
+class FlashDebertaV2PreTrainedModel(DebertaV2PreTrainedModel):
+    """Same role as src/flashdeberta/model.py:312-392 (weight init and loading are transformers')."""
+    config_class = DebertaV2Config
+
+
+class FlashDebertaV2Model(DebertaV2Model):
+    """src/flashdeberta/model.py:394-496."""
+
+    def __init__(self, config):
+        super().__init__(config)
+        self.encoder = FlashDebertaV2Encoder(config)
+        self.post_init()
+
+    def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
+                token_type_ids: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
+                inputs_embeds: Optional[torch.Tensor] = None, output_attentions: Optional[bool] = None,
+                output_hidden_states: Optional[bool] = None, return_dict: Optional[bool] = None, **kwargs):
+        if self.z_steps > 1 and self.encoder._fused:
+            raise NotImplementedError("z_steps > 1 is not supported with the fused attention backend")
+        return super().forward(input_ids=input_ids, attention_mask=attention_mask, token_type_ids=token_type_ids,
+                               position_ids=position_ids, inputs_embeds=inputs_embeds,
+                               output_attentions=output_attentions, output_hidden_states=output_hidden_states,
+                               return_dict=return_dict, **kwargs)
+
+
+def _with_flash_backbone(hf_cls, doc):
+    class _Head(hf_cls):
+        def __init__(self, config):
+            super().__init__(config)
+            self.deberta = FlashDebertaV2Model(config)
+            self.post_init()
+
+    _Head.__name__ = _Head.__qualname__ = "Flash" + hf_cls.__name__
+    _Head.__doc__ = doc
+    return _Head
+
+
+FlashDebertaV2ForMaskedLM = _with_flash_backbone(DebertaV2ForMaskedLM, "src/flashdeberta/model.py:498-606")
+FlashDebertaV2ForSequenceClassification = _with_flash_backbone(
+    DebertaV2ForSequenceClassification, "src/flashdeberta/model.py:608-698")
+FlashDebertaV2ForTokenClassification = _with_flash_backbone(
+    DebertaV2ForTokenClassification, "src/flashdeberta/model.py:700-757")
+FlashDebertaV2ForQuestionAnswering = _with_flash_backbone(
+    DebertaV2ForQuestionAnswering, "src/flashdeberta/model.py:759-843")
+FlashDebertaV2ForMultipleChoice = _with_flash_backbone(
+    DebertaV2ForMultipleChoice, "src/flashdeberta/model.py:845-920")

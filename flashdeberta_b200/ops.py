@@ -24,6 +24,7 @@ __all__ = [
 
 _status: Dict[str, torch.Tensor] = {}
 _launches = 0  # kernels this module asked the library to launch (the benchmark reports it)
+event_log = None  # set to a list to have every fused-attention call append its (start, end) CUDA events
 
 
 def launch_count() -> int:
@@ -182,7 +183,13 @@ def disentangled_attention(
         base = (ws.data_ptr() + 255) & ~255
         p.workspace, p.workspace_bytes = base, need
         stream = torch.cuda.current_stream(q.device).cuda_stream
+        if event_log is not None:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         _lib.check(lib.fdb_attn_fwd(C.byref(p), C.c_void_p(stream)))
+        if event_log is not None:
+            ev1.record()
+            event_log.append((ev0, ev1))
         _launches += 2 + int(pos_key is not None or pos_query is not None)
         # `keep` and `ws` were allocated on this stream, so the caching allocator reuses them in stream order
         del keep, ws

@@ -1,0 +1,138 @@
+"""CPU-only checks of the C ABI: the library loads, exports what the header declares, the struct layouts agree,
+the integer bucket table is bit-exact against the HuggingFace fixtures, and argument errors are reported before any
+launch."""
+import ctypes as C
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from flashdeberta_b200 import _lib, bucket
+from flashdeberta_b200.attention import lengths_from_mask
+from tests._golden import load_bucket_golden
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "fdb_b200.h")
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    lib = _lib.load()
+    text = open(HEADER).read()
+    declared = set(re.findall(r"FDB_API[^;(]*?\b(fdb_[a-z0-9_]+)\s*\(", text))
+    assert declared, "no declarations found in the header"
+    assert declared == set(_lib.EXPORTS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.fdb_abi_version() == _lib.ABI_VERSION
+
+
+def test_struct_layout_matches_the_header(tmp_path):
+    fields = [f[0] for f in _lib.AttnParams._fields_]
+    src = tmp_path / "layout.c"
+    body = "\n".join(f'  printf("{f} %zu\\n", offsetof(fdb_attn_params, {f}));' for f in fields)
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "fdb_b200.h"\nint main(void) {\n'
+        '  printf("sizeof %zu\\n", sizeof(fdb_attn_params));\n' + body + "\n  return 0;\n}\n")
+    exe = tmp_path / "layout"
+    subprocess.check_call(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    out = dict(line.split() for line in subprocess.check_output([str(exe)], text=True).splitlines())
+    assert int(out["sizeof"]) == C.sizeof(_lib.AttnParams)
+    for f in fields:
+        assert int(out[f]) == getattr(_lib.AttnParams, f).offset, f
+
+
+def _configs(g):
+    for k in g:
+        if k.startswith("idx_"):
+            _, b, m = k.split("_")
+            yield int(b), int(m)
+
+
+def test_bucket_table_bit_exact_vs_hf_fixture():
+    g = load_bucket_golden()
+    d_lo, d_hi = int(g["d_lo"]), int(g["d_hi"])
+    for buckets, max_rel in _configs(g):
+        want = g[f"idx_{buckets}_{max_rel}"].astype(np.int64)
+        tab, d_min = bucket.host_lut(buckets, max_rel)
+        d = np.arange(d_lo, d_hi + 1)
+        got = tab[np.clip(d - d_min, 0, len(tab) - 1)].astype(np.int64)
+        assert np.array_equal(got, want), (buckets, max_rel)
+        # the saturation claim: first/last entries hold beyond the table
+        assert tab[0] == want[0] and tab[-1] == want[-1]
+        for dist in (-40000, -513, -512, -129, -1, 0, 1, 128, 129, 505, 506, 40000):
+            assert bucket.relative_index(dist, buckets, max_rel) == want[dist - d_lo]
+
+
+def test_v3_table_shape():
+    tab, d_min = bucket.host_lut(256, 512)
+    assert (len(tab), d_min, int(tab[0]), int(tab[-1])) == (1019, -512, 0, 511)
+    assert np.all(np.diff(tab.astype(np.int32)) >= 0)
+
+
+def _params(**kw):
+    p = _lib.AttnParams()
+    p.struct_bytes = C.sizeof(_lib.AttnParams)
+    p.dtype = _lib.FDB_BF16
+    p.q = p.k = p.v = p.out = 0x1000
+    for n in ("q", "k", "v"):
+        setattr(p, n + "_row_stride", 128)
+        setattr(p, n + "_head_stride", 64)
+    p.out_row_stride, p.out_head_stride = 128, 64
+    p.batch, p.max_seqlen, p.total_rows, p.heads, p.head_dim = 2, 64, 128, 2, 64
+    p.sm_scale = 0.125
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("change,code", [
+    (dict(struct_bytes=8), -1),
+    (dict(q=0), -1),
+    (dict(head_dim=128), -2),
+    (dict(dtype=_lib.FDB_FP32), -2),
+    (dict(dtype=7), -1),
+    (dict(q=0x1008), -3),
+    (dict(q_row_stride=130), -3),
+    (dict(total_rows=100), -1),
+    (dict(sm_scale=0.0), -1),
+    (dict(pos_key=0x2000), -1),       # tables without a bucket table
+    (dict(seq_lens=0x10, cu_seqlens=0x10), -1),
+])
+def test_argument_errors_are_reported_before_any_launch(change, code):
+    lib = _lib.load()
+    p = _params(**change)
+    assert lib.fdb_attn_fwd(C.byref(p), None) == code
+    assert lib.fdb_last_error().decode() != ""
+    with pytest.raises(_lib.FdbError):
+        _lib.check(lib.fdb_attn_fwd(C.byref(p), None))
+
+
+def test_missing_workspace_is_an_error():
+    lib = _lib.load()
+    p = _params()
+    need = lib.fdb_attn_workspace_bytes(C.byref(p))
+    assert need > 0 and need % 256 == 0
+    assert lib.fdb_attn_fwd(C.byref(p), None) == -4
+
+
+def test_lengths_from_every_mask_form():
+    m2 = torch.tensor([[1, 1, 1, 0], [1, 0, 0, 0], [0, 0, 0, 0]])
+    want = [3, 1, 0]
+    assert lengths_from_mask(m2).tolist() == want
+    ext = m2.unsqueeze(1).unsqueeze(2)
+    m4 = ext * ext.squeeze(-2).unsqueeze(-1)
+    assert lengths_from_mask(m4).tolist() == want
+    assert lengths_from_mask(m4[:, 0]).tolist() == want
+    assert lengths_from_mask(torch.tensor(want)).tolist() == want
+    assert lengths_from_mask(None) is None
+
+
+def test_ops_refuse_cpu_tensors():
+    from flashdeberta_b200 import ops
+    x = torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.disentangled_attention(x, x, x, None, None, max_seqlen=8)
