@@ -1,0 +1,69 @@
+"""Attention-only microbenchmark of the fused kernel (CUDA events, inputs rotated so consecutive launches do not find
+their operands in L2).
+
+    python -m flashdeberta_b200.microbench --batch 8 --seq 2048 --heads 12 [--iters 30] [--no-pos] [--packed-lens 700,130]
+
+Prints one JSON line: median/min ms per launch and algorithmic TFLOP/s (4*l^2*D + 2*l*2S*D per position term, per
+sequence and head).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+from . import ops
+
+
+def attn_flops(lengths, heads, head_dim=64, span=256, c2p=True, p2c=True):
+    return sum(heads * (4 * n * n * head_dim + (int(c2p) + int(p2c)) * 2 * n * 2 * span * head_dim) for n in lengths)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=12)
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated between launches")
+    ap.add_argument("--no-pos", action="store_true")
+    ap.add_argument("--valid", type=int, default=0, help="valid length of every sequence (default: all)")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    B, L, H, D = args.batch, args.seq, args.heads, 64
+    g = torch.Generator(device="cpu").manual_seed(0)
+    sets = []
+    for _ in range(args.sets):
+        q, k, v = (torch.randn(B, L, H, D, generator=g).bfloat16().to(dev) for _ in range(3))
+        sets.append((q, k, v))
+    pk = pq = None
+    if not args.no_pos:
+        pk, pq = (torch.randn(H, 512, D, generator=g).mul_(0.5).bfloat16().to(dev) for _ in range(2))
+    lens = [args.valid or L] * B
+    kw = dict(max_seqlen=L, position_buckets=256, max_relative_positions=512)
+    if args.valid:
+        kw["seq_lens"] = torch.tensor(lens, dtype=torch.int32, device=dev)
+    for i in range(args.warmup):
+        ops.disentangled_attention(*sets[i % args.sets], pk, pq, **kw)
+    torch.cuda.synchronize()
+    times = []
+    for i in range(args.iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.disentangled_attention(*sets[i % args.sets], pk, pq, **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ops.check_status()
+    f = attn_flops(lens, H, c2p=not args.no_pos, p2c=not args.no_pos)
+    med, mn = statistics.median(times), min(times)
+    print(json.dumps({"batch": B, "seq": L, "heads": H, "valid": lens[0], "pos": not args.no_pos, "ms_median": med,
+                      "ms_min": mn, "tflops_median": f / med / 1e9, "tflops_best": f / mn / 1e9,
+                      "flops": f, "l2": f"{args.sets} input sets rotated ({args.sets * 3 * B * L * H * D * 2 >> 20} MiB)"}))
+
+
+if __name__ == "__main__":
+    main()
