@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libfdb_b200.so")
 FDB_OK = 0
 FDB_BF16, FDB_FP32, FDB_E4M3 = 0, 1, 2
 FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN = 1, 2
+STATIC_SCRATCH_BYTES = 8 << 20
 ABI_VERSION = 1
 
 
@@ -43,7 +44,7 @@ class AttnParams(C.Structure):
 
 EXPORTS = (
     "fdb_abi_version", "fdb_last_error", "fdb_status_string", "fdb_build_bucket_lut", "fdb_relative_index",
-    "fdb_attn_workspace_bytes", "fdb_attn_fwd", "fdb_attn_fwd_check", "fdb_relative_index_matrix",
+    "fdb_attn_workspace_bytes", "fdb_attn_fwd", "fdb_attn_fwd_static", "fdb_attn_fwd_check", "fdb_relative_index_matrix",
     "fdb_quantize_e4m3",
 )
 
@@ -80,6 +81,8 @@ def load() -> C.CDLL:
     lib.fdb_attn_workspace_bytes.argtypes = [C.POINTER(AttnParams)]
     lib.fdb_attn_fwd.restype = C.c_int
     lib.fdb_attn_fwd.argtypes = [C.POINTER(AttnParams), C.c_void_p]
+    lib.fdb_attn_fwd_static.restype = C.c_int
+    lib.fdb_attn_fwd_static.argtypes = [C.POINTER(AttnParams), C.c_void_p]
     lib.fdb_attn_fwd_check.restype = C.c_int
     lib.fdb_attn_fwd_check.argtypes = [C.POINTER(AttnParams), C.c_void_p]
     lib.fdb_relative_index_matrix.restype = C.c_int

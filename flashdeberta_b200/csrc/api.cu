@@ -23,7 +23,7 @@ void clear_error() { g_error[0] = 0; }
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Checks shared by the fused and the check kernel.  `fused` adds the layout rules TMA imposes.
-static int validate(const fdb_attn_params* p, bool fused) {
+int validate(const fdb_attn_params* p, bool fused) {
   if (p == nullptr) return fail(FDB_ERR_INVALID_ARGUMENT, "params is NULL");
   if (p->struct_bytes != sizeof(fdb_attn_params))
     return fail(FDB_ERR_INVALID_ARGUMENT, "struct_bytes is %u, this library expects %zu (ABI %d)", p->struct_bytes,

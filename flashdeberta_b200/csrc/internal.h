@@ -11,6 +11,8 @@ namespace fdb {
 // ---- error text (thread-local) -------------------------------------------------------------------------------------
 int fail(int code, const char* fmt, ...);
 void clear_error();
+// argument checks shared by the entry points; `fused` adds the layout rules of the tensor-core kernel
+int validate(const fdb_attn_params* p, bool fused);
 
 // ---- bucket table (host) -------------------------------------------------------------------------------------------
 int64_t signed_bucket(int32_t bucket_size, int32_t max_position, int64_t rel);

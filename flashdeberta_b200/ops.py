@@ -18,7 +18,7 @@ import torch
 from . import _lib, bucket
 
 __all__ = [
-    "disentangled_attention", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3",
+    "disentangled_attention", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3",
     "check_status", "launch_count",
 ]
 
@@ -194,6 +194,35 @@ def disentangled_attention(
         # `keep` and `ws` were allocated on this stream, so the caching allocator reuses them in stream order
         del keep, ws
     return (out, lse) if return_lse else out
+
+
+def disentangled_attention_static(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    pos_key: Optional[torch.Tensor], pos_query: Optional[torch.Tensor],
+    *, out: torch.Tensor, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
+    max_seqlen: int, sm_scale: Optional[float] = None, position_buckets: int = -1, max_relative_positions: int = -1,
+) -> torch.Tensor:
+    """The fused kernel through ``fdb_attn_fwd_static``: no workspace is allocated here or in the library; the scratch
+    is the library's built-in per-device array (``_lib.STATIC_SCRATCH_BYTES``).  For callers that must not allocate on
+    the device at call time; ``out`` (bf16, q's shape, contiguous) is supplied by the caller for the same reason.
+    Calls on one device share that array, so keep them ordered on one stream.  Larger problems raise FdbError
+    (code -6)."""
+    global _launches
+    if not q.is_cuda:
+        raise RuntimeError("flashdeberta_b200 runs on CUDA devices only; there is no CPU path")
+    if out.dtype != torch.bfloat16 or out.shape != q.shape or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 tensor of q's shape")
+    lib = _lib.load()
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1] * (1 + int(pos_key is not None) + int(pos_query is not None)))
+    with torch.cuda.device(q.device):
+        p, keep = _fill_params(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale,
+                               position_buckets, max_relative_positions, out, None)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        _lib.check(lib.fdb_attn_fwd_static(C.byref(p), C.c_void_p(stream)))
+        _launches += 2 + int(pos_key is not None or pos_query is not None)
+        del keep
+    return out
 
 
 def disentangled_attention_check(

@@ -154,6 +154,31 @@ FDB_API uint64_t fdb_attn_workspace_bytes(const fdb_attn_params* p);
 FDB_API int fdb_attn_fwd(const fdb_attn_params* p, void* stream);
 
 /*
+ * fdb_attn_fwd for callers that cannot give it a workspace.  (No counterpart in the reference: its launchers
+ * allocate through torch on every call.)
+ *
+ * Some hosts of this library have no way to allocate device memory at the point where they call it: an inference
+ * server that handed the whole GPU to its own arena at start-up, a plug-in running inside someone else's stream
+ * callback or latency-critical loop where cudaMalloc/cudaFree (which synchronise the device) are forbidden, or a
+ * C host that simply has no allocator wired to this GPU.  For them this entry point keeps the scratch that
+ * fdb_attn_fwd needs (sequence table, tile prefix, the two expanded position tables) in a fixed array that lives
+ * inside the library image on the device: FDB_STATIC_SCRATCH_BYTES per GPU that loads the library, held until the
+ * process exits.  p->workspace and p->workspace_bytes are ignored; inputs, output and the status word are still the
+ * caller's.  It calls no cudaMalloc, cudaFree or any other allocating routine.
+ *
+ * Limits and rules:
+ *  - parameters whose scratch need (fdb_attn_workspace_bytes) exceeds FDB_STATIC_SCRATCH_BYTES are refused with
+ *    FDB_ERR_LIMIT and nothing is launched (DeBERTa-v3 geometry: up to 16 heads and tens of thousands of sequences fit);
+ *  - the first call on each device looks the array's device address up once (with that device current); make that
+ *    first call outside any stream capture;
+ *  - every call on a device uses the same array and leaves its contents behind.  The kernels rewrite every byte
+ *    they later read, so nothing has to be cleared between calls, but two calls that overlap on the GPU (different
+ *    streams, or different host threads without ordering) race on it: keep calls on one device ordered.
+ */
+#define FDB_STATIC_SCRATCH_BYTES (8u << 20)
+FDB_API int fdb_attn_fwd_static(const fdb_attn_params* p, void* stream);
+
+/*
  * Check kernel: the same contract computed with fp32 arithmetic on CUDA cores, one warp per (row, head), no
  * tensor cores, bucket index looked up per element from bucket_lut.  bf16 or fp32 inputs, head_dim <= 128.
  * Needs no workspace.  For validation, never for speed.
