@@ -1,63 +1,82 @@
-// Fused DeBERTa disentangled-attention forward for sm_100a.
+// Fused DeBERTa disentangled-attention forward for sm_100a — warp-specialised kernel.
 //
-// One CTA = one 128-row query tile of one (sequence, head).  It loops over 128-key tiles; per tile:
-//   S   = Q.K^T                      tcgen05.mma, operands staged by TMA (128-byte swizzle), accumulator in TMEM
-//   S  += c2p + p2c                  (below)
-//   P   = exp2(S*scale*log2e - m)    one thread per row, S read from TMEM with tcgen05.ld
-//   O  += P.V                        tcgen05.mma, P written to shared memory in the operand layout, O stays in TMEM and is
-//                                    only rescaled when the running maximum moved by more than 2^8
-// which replaces the reference's Triton forward kernels (src/flashdeberta/ops/flash_attention.py:146-300 and
+// Replaces the reference's Triton forward kernels (src/flashdeberta/ops/flash_attention.py:146-300 and
 // src/flashdeberta/ops/flash_attention_varlen.py:85-225) and the two bias GEMMs in front of them
 // (src/flashdeberta/model.py:189-192, :210-214).
 //
-// Position terms.  The tables arrive already expanded through the bucket function (see attn_prepare.cu), so the row a
-// score element (m, n) needs is (m - n) - d_first and a tile pair needs 255 consecutive rows.  Three kinds of tile pair:
-//   * every distance at or beyond the upper saturation point: c2p is one dot product per query row (added to the
-//     row's exponent offset, no per-element work) and p2c is one dot product per key, obtained on the tensor core by
-//     accumulating  R.K^T  into S, where every row of R is the saturated pos_query row;
-//   * every distance at or below the lower saturation point: the same with the other end of the tables;
-//   * otherwise ("band"): X_k.Q^T (256x128) and K.X_q^T (128x256) are computed on the tensor core from the staged
-//     windows X_k, X_q, drained to shared memory as bf16, and each thread picks  c2p[m][m-n]  and  p2c[n][m-n]  with
-//     plain indexed shared loads whose offsets are compile-time constants relative to a per-thread base.
+// One CTA = one 128-row query tile of one (sequence, head); 12 warps (registers move from the producer warpgroup to the
+// softmax warpgroups with setmaxnreg):
+//   warps 0-3  softmax group 0: thread r owns row r of the tile, keys   0..63  of every 128-key tile
+//   warps 4-7  softmax group 1: thread r owns row r of the tile, keys  64..127
+//   warp  8    lane 0 issues every tcgen05.mma (and allocates tensor memory)
+//   warp  9    lane 0 issues every TMA load: Q once, K/V double-buffered, position-table windows
+// Per key tile:  S = Q.K^T  (tensor core, fp32 in TMEM)  ->  the two groups read their halves of S with tcgen05.ld, add the
+// position terms, agree on the row maximum through shared memory, write P = exp2(...) as bf16 back into tensor memory over
+// their own S columns  ->  O += P.V with P read from tensor memory and V from shared memory.  S is double-buffered, so the
+// scores of tile j+1 are computed while the softmax of tile j runs.  O stays in TMEM and is rescaled only when the running
+// maximum moved by more than 2^8.
+//
+// Position terms (tables arrive expanded through the bucket function, see attn_prepare.cu; row of (m, n) is (m-n)-d_first):
+//   * saturated tile pair (all distances beyond a saturation point): c2p is one dot product per query row, folded into the
+//     row's exponent offset; p2c is one dot product per key, accumulated into S on the tensor core as R.K^T where all rows
+//     of R equal the saturated pos_query row (R is 8 rows of shared memory read with a zero group stride);
+//   * band tile pair: p2c comes from eight 128x32 products X_q[32(3-b+t) ..].K[32b ..]^T, b = key block, t = 0/1, arranged so
+//     that the value thread (quadrant w, lane l) needs for key 32b+c sits in its own quadrant at lane (l+31-c)&31 of product
+//     t = (l > c): one select on the source side and one warp shuffle per score element, fp32, no shared memory;
+//     c2p needs a transpose: X_k[window].Q^T (256x128) is drained from TMEM to shared memory as bf16 [position][query] and
+//     thread m reads c2p[m][m+127-i] at compile-time offsets from a per-thread base.
 // No (rows x 2*span) bias tensor is ever written to global memory.
 //
-// Every mbarrier wait is bounded; when one gives up the CTA stops issuing work, sets FDB_DEV_TIMEOUT in the status
-// word, releases its TMEM and returns.
+// Every mbarrier wait is bounded and gives up early once another role has raised the abort flag; the CTA then sets
+// FDB_DEV_TIMEOUT in the status word, waits a millisecond for copies in flight, releases its TMEM and returns.
+// No TMA load uses multicast.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "internal.h"
 #include "sm100_ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace fdb {
 namespace {
 
 using namespace ptx;
 
-constexpr int kThreads = 128;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = 384;           // three warpgroups: two softmax groups and one producer group (warps 10, 11 idle)
+constexpr int kMmaWarp = 8, kTmaWarp = 9;
+constexpr int kProducerRegs = 56, kSoftmaxRegs = 224;  // 168 * 384 = 40 * 128 + 232 * 256
 constexpr uint32_t kTmemCols = 512;
-// TMEM columns
-constexpr uint32_t kColO = 0;       // 64 columns: output accumulator
-constexpr uint32_t kColS = 64;      // 128 columns: scores
-constexpr uint32_t kColBias = 192;  // 256 columns: position products of a band tile
+// TMEM columns: O 64 | R 256 (position products of a band tile; its upper half doubles as S buffer 1) | S buffer 0
+constexpr uint32_t kColO = 0;
+constexpr uint32_t kColR = 64;
+constexpr uint32_t kColS1 = 192;
+constexpr uint32_t kColS0 = 320;
 
 // shared memory map (bytes from a 1024-aligned base)
-constexpr uint32_t kSmemQ = 0;                       // 128 x 128 B
-constexpr uint32_t kSmemK = 16384;                   // 128 x 128 B
-constexpr uint32_t kSmemV = 32768;                   // 128 x 128 B
-constexpr uint32_t kSmemP = 49152;                   // 2 x (128 x 128 B): keys 0-63, keys 64-127
-constexpr uint32_t kSmemWinK = 81920;                // 256 x 128 B window of expanded pos_key
-constexpr uint32_t kSmemWinQ = kSmemWinK + 32768;    // 256 x 128 B window of expanded pos_query
-constexpr uint32_t kStageCPitch = 272;               // c2p stage: [256 positions][128 query rows] bf16, padded rows
-constexpr uint32_t kSmemStageC = kSmemWinK;          // overlays both windows (dead once the position MMAs finished)
-constexpr uint32_t kStagePPitch = 528;               // p2c stage: [128 keys][256 positions] bf16, padded rows
-constexpr uint32_t kSmemStageP = kSmemStageC + 256 * kStageCPitch;  // 151552
-constexpr uint32_t kSmemSat = kSmemWinK;             // 128 x 128 B tile whose rows all equal one pos_query row
-constexpr uint32_t kSmemBars = kSmemStageP + 128 * kStagePPitch;    // 219136
-constexpr uint32_t kSmemBytes = kSmemBars + 128 + 1024;             // + alignment slack
-static_assert(kSmemStageP == 151552 && kSmemBars == 219136, "shared memory map");
+constexpr uint32_t kSmemQ = 0;                      // 128 x 128 B
+constexpr uint32_t kSmemK = 16384;                  // 2 stages
+constexpr uint32_t kSmemV = 49152;                  // 2 stages
+constexpr uint32_t kSmemWinK = 81920;               // 256 x 128 B window of expanded pos_key
+constexpr uint32_t kSmemWinQ = 114688;              // 256 x 128 B window of expanded pos_query
+constexpr uint32_t kStageCPitch = 272;              // c2p stage [256 positions][128 query rows] bf16, rows padded by 16 B
+constexpr uint32_t kSmemStageC = 147456;
+constexpr uint32_t kSmemSat = kSmemStageC + 256 * kStageCPitch;  // 217088: 2 x (8 x 128 B) saturated pos_query rows (hi, lo)
+constexpr uint32_t kSmemXchg = kSmemSat + 2048;     // float [2 parities][2 groups][128 rows] row maxima
+constexpr uint32_t kSmemLsum = kSmemXchg + 2048;    // float [2 groups][128 rows] row sums at the end
+constexpr uint32_t kSmemBars = kSmemLsum + 1024;
+constexpr uint32_t kSmemBytes = kSmemBars + 256 + 1024;  // + alignment slack
+static_assert(kSmemSat == 217088, "shared memory map");
 static_assert(kSmemBytes <= 232448, "exceeds 227 KB");
+
+enum Bar : uint32_t {
+  kBarQ = 0, kBarK = 1, kBarV = 3, kBarKFree = 5, kBarVFree = 7, kBarWin = 9, kBarWinFree = 10, kBarS = 11, kBarP = 13,
+  kBarO = 15, kBarR = 16, kBarRFree = 17, kNumBars = 18
+};
 
 struct alignas(64) FwdArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_xk, tm_xq;
@@ -77,7 +96,6 @@ struct alignas(64) FwdArgs {
 enum TileKind : int { kPlain = 0, kSatHi = 1, kSatLo = 2, kBand = 3 };
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
-
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
@@ -91,8 +109,16 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
 
-// dot product of this thread's query row (swizzled in shared memory) with one 64-element bf16 row in global memory
+// dot product of one query row (128-byte-swizzled in shared memory) with one 64-element bf16 row in global memory
 __device__ __forceinline__ float dot_q_row(uint32_t q_row_addr, int row, const __nv_bfloat16* __restrict__ g) {
   float acc = 0.f;
   const uint4* g4 = reinterpret_cast<const uint4*>(g);
@@ -110,11 +136,23 @@ __device__ __forceinline__ float dot_q_row(uint32_t q_row_addr, int row, const _
   return acc;
 }
 
+// Which S buffer a tile uses and the parity of that buffer's barriers for this use.  Band tiles always take buffer 0
+// (buffer 1 lies inside the position-product area).  Every role walks the tiles in order with its own copy.
+struct BufState {
+  int cur = 0;
+  uint32_t uses[2] = {0u, 0u};
+  __device__ __forceinline__ void next(bool band, int& buf, uint32_t& parity) {
+    if (band) { buf = 0; cur = 1; } else { buf = cur; cur ^= 1; }
+    parity = uses[buf] & 1u;
+    ++uses[buf];
+  }
+};
+
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_constant__ FwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y;
 
   // ---- which tile ------------------------------------------------------------------------------------------------
@@ -131,15 +169,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   const int len = __ldg(args.seq_info + 2 * seq + 1);
   // rows of this tile that may be written: packed -> the sequence's own rows; dense -> the padded row range
   const int row_limit = args.packed ? len : args.max_seqlen;
-  const int my_row = m0 + tid;  // position inside the sequence
-  __nv_bfloat16* out_ptr = args.out + (int64_t)(seq_row0 + my_row) * args.o_rs + (int64_t)head * args.o_hs;
 
   if (m0 >= len) {  // dense padding tile: zeros, nothing else (src/flashdeberta/padding.py:30-44)
-    if (my_row < row_limit) {
-      uint4* o4 = reinterpret_cast<uint4*>(out_ptr);
+    if (tid < kTileM && m0 + tid < row_limit) {
+      uint4* o4 = reinterpret_cast<uint4*>(args.out + (int64_t)(seq_row0 + m0 + tid) * args.o_rs + (int64_t)head * args.o_hs);
 #pragma unroll
       for (int c = 0; c < 8; ++c) o4[c] = make_uint4(0, 0, 0, 0);
-      if (args.lse != nullptr) args.lse[(int64_t)(seq_row0 + my_row) * args.heads + head] = 0.f;
+      if (args.lse != nullptr) args.lse[(int64_t)(seq_row0 + m0 + tid) * args.heads + head] = 0.f;
     }
     return;
   }
@@ -147,411 +183,407 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   const bool has_c2p = args.xk != nullptr, has_p2c = args.xq != nullptr;
   const bool has_pos = has_c2p || has_p2c;
   const int num_kt = (len + kTileN - 1) / kTileN;
+  auto tile_kind = [&](int j) -> int {
+    if (!has_pos) return kPlain;
+    const int d0 = m0 - j * kTileN - (kTileN - 1);  // smallest distance of the pair; the largest is d0 + 254
+    return d0 >= args.sat_hi ? kSatHi : (d0 + 254 <= args.sat_lo ? kSatLo : kBand);
+  };
 
-  // ---- barriers, TMEM ----------------------------------------------------------------------------------------------
-  const uint32_t bar_q = smem + kSmemBars + 0, bar_k = smem + kSmemBars + 8, bar_v = smem + kSmemBars + 16,
-                 bar_win = smem + kSmemBars + 24, bar_s = smem + kSmemBars + 32, bar_pv = smem + kSmemBars + 40;
-  const uint32_t tmem_slot = smem + kSmemBars + 64;
+  auto bar = [&](uint32_t i) -> uint32_t { return smem + kSmemBars + 8u * i; };
+  const uint32_t tmem_slot = smem + kSmemBars + 8u * kNumBars;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 8u * kNumBars + 8u);
+
+  // ---- set-up ---------------------------------------------------------------------------------------------------------
   if (tid == 0) {
-    *reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 72) = 0u;
-    mbar_init(bar_q, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
-    mbar_init(bar_win, 1); mbar_init(bar_s, 1); mbar_init(bar_pv, 1);
+    *abort_flag = 0u;
+    for (uint32_t i = 0; i < kNumBars; ++i) {
+      const uint32_t count = (i == kBarP || i == kBarP + 1 || i == kBarRFree) ? kSoftmaxThreads : 1u;
+      mbar_init(bar(i), count);
+    }
     fence_barrier_init();
-    tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
   }
-  if (warp == 0) {
+  if (has_p2c && tid < 128) {
+    // saturated pos_query rows, 8 identical 128-byte rows each, in the swizzled operand layout: tile 0 = last row, 1 = first
+    const int t = tid >> 6, row = (tid >> 3) & 7, c = tid & 7;
+    const __nv_bfloat16* src = args.xq + ((int64_t)head * args.xrows + (t == 0 ? args.xrows - 1 : 0)) * kHeadDim;
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + c);
+    sts_v4(smem + kSmemSat + t * 1024 + row * 128 + (uint32_t(c ^ row) << 4), v.x, v.y, v.z, v.w);
+    fence_proxy_async_smem();
+  }
+  if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 64);
-  const uint32_t tmem_lane = tmem_base + (uint32_t(warp * 32) << 16);  // this warp's 32 lanes
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 8u * kNumBars);
+  auto sbuf_col = [&](int b) -> uint32_t { return b == 0 ? kColS0 : kColS1; };
 
-  // `ok` turns false once a bounded wait gave up.  It is kept warp-uniform (the collective tcgen05 loads and stores
-  // below must be executed by whole warps) and becomes CTA-uniform at every sync_check().
   bool ok = true;
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 72);
-  auto wait_all = [&](uint32_t bar, uint32_t parity) { ok = __all_sync(0xffffffffu, ok && mbar_wait(bar, parity)); };
-  auto wait_one = [&](uint32_t bar, uint32_t parity) -> bool {  // used by thread 0 alone; reported at the next sync_check()
-    const bool r = mbar_wait(bar, parity);
-    if (!r) *abort_flag = 1u;
-    return r;
-  };
-  auto sync_check = [&]() {
-    __syncthreads();
-    ok = ok && (*abort_flag == 0u);
-  };
-  uint32_t ph_k = 0, ph_v = 0, ph_win = 0, ph_s = 0, ph_pv = 0;
 
-  // ---- first loads ---------------------------------------------------------------------------------------------------
-  if (tid == 0) {
-    mbar_expect_tx(bar_q, 16384);
-    tma_load_3d(smem + kSmemQ, &args.tm_q, bar_q, 0, head, seq_row0 + m0);
-    mbar_expect_tx(bar_k, 16384);
-    tma_load_3d(smem + kSmemK, &args.tm_k, bar_k, 0, head, seq_row0);
-    mbar_expect_tx(bar_v, 16384);
-    tma_load_3d(smem + kSmemV, &args.tm_v, bar_v, 0, head, seq_row0);
-  }
-  wait_all(bar_q, 0);  // every thread reads its Q row below
-
-  // Saturated c2p terms of this thread's row: Q[m].X_k[first row] and Q[m].X_k[last row].
-  float rc_lo = 0.f, rc_hi = 0.f;
-  if (has_c2p && ok) {
-    const __nv_bfloat16* xk_h = args.xk + (int64_t)head * args.xrows * kHeadDim;
-    const uint32_t q_row = smem + kSmemQ + uint32_t(tid) * 128u;
-    rc_lo = dot_q_row(q_row, tid, xk_h);
-    rc_hi = dot_q_row(q_row, tid, xk_h + (int64_t)(args.xrows - 1) * kHeadDim);
-  }
-
-  const uint32_t idesc_s = instr_desc(128, 128, 1, 0, 0);
-  const uint32_t idesc_p2c = instr_desc(128, 256, 1, 0, 0);
-  const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
-
-  float m_used = 0.f, l_run = 0.f;
-  int sat_built = kPlain;  // which saturated pos_query tile currently sits in kSmemSat
-
-  for (int j = 0; j < num_kt; ++j) {
-    const int n0 = j * kTileN;
-    const int d0 = m0 - n0 - (kTileN - 1);  // smallest distance of the tile pair; largest is d0 + 254
-    int kind = kPlain;
-    if (has_pos) kind = d0 >= args.sat_hi ? kSatHi : (d0 + 254 <= args.sat_lo ? kSatLo : kBand);
-
-    if (kind == kBand) {
-      // ---- position products on the tensor core, drained to shared memory as bf16 ------------------------------
-      // Order matters for shared memory: the c2p stage overlays both windows, so the p2c product (which reads the
-      // pos_query window) is computed and drained first.
-      if (tid == 0 && ok) {
-        const int u0 = d0 - args.d_first;
-        mbar_expect_tx(bar_win, (has_c2p ? 32768u : 0u) + (has_p2c ? 32768u : 0u));
-        if (has_c2p) tma_load_3d(smem + kSmemWinK, &args.tm_xk, bar_win, 0, u0, head);
-        if (has_p2c) tma_load_3d(smem + kSmemWinQ, &args.tm_xq, bar_win, 0, u0, head);
-        const bool ready = wait_one(bar_win, ph_win) && wait_one(bar_k, ph_k);
-        tc_fence_after();
-        if (ready && has_p2c) {
-          // p2c[n][j] = K[n].X_q[j]   -> 256 columns of the bias area
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_bf16(tmem_base + kColBias, smem_desc_sw128(smem + kSmemK + ks * 32, 1024, 16),
-                     smem_desc_sw128(smem + kSmemWinQ + ks * 32, 1024, 16), idesc_p2c, ks > 0);
+  if (warp >= kMmaWarp) {
+  reg_dealloc<kProducerRegs>();
+  if (warp == kTmaWarp) {
+    // =================================================== TMA producer ===================================================
+    if (lane == 0) {
+      auto wait = [&](uint32_t b, uint32_t parity) {
+        if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
+      };
+      tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
+      mbar_expect_tx(bar(kBarQ), 16384);
+      tma_load_3d(smem + kSmemQ, &args.tm_q, bar(kBarQ), 0, head, seq_row0 + m0);
+      int band_idx = 0;
+      for (int j = 0; j < num_kt; ++j) {
+        const int s = j & 1;
+        const uint32_t use = uint32_t(j >> 1);  // how often this stage was used before
+        if (j >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
+        if (!ok) break;
+        mbar_expect_tx(bar(kBarK + s), 16384);
+        tma_load_3d(smem + kSmemK + s * 16384, &args.tm_k, bar(kBarK + s), 0, head, seq_row0 + j * kTileN);
+        if (tile_kind(j) == kBand) {
+          if (band_idx > 0) wait(bar(kBarWinFree), uint32_t(band_idx - 1) & 1u);
+          if (!ok) break;
+          const int u0 = m0 - j * kTileN - (kTileN - 1) - args.d_first;
+          mbar_expect_tx(bar(kBarWin), (has_c2p ? 32768u : 0u) + (has_p2c ? 32768u : 0u));
+          if (has_c2p) tma_load_3d(smem + kSmemWinK, &args.tm_xk, bar(kBarWin), 0, u0, head);
+          if (has_p2c) tma_load_3d(smem + kSmemWinQ, &args.tm_xq, bar(kBarWin), 0, u0, head);
+          ++band_idx;
         }
-        mma_commit(bar_s);
+        if (j >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
+        if (!ok) break;
+        mbar_expect_tx(bar(kBarV + s), 16384);
+        tma_load_3d(smem + kSmemV + s * 16384, &args.tm_v, bar(kBarV + s), 0, head, seq_row0 + j * kTileN);
       }
-      ph_win ^= 1;
-      wait_all(bar_s, ph_s); ph_s ^= 1;
-      wait_all(bar_pv, ph_pv ^ 1);  // previous P.V (if any) is done as well: P and the stage area are free
-      tc_fence_after();
-      if (has_p2c && ok) {
-        const uint32_t row_addr = smem + kSmemStageP + uint32_t(tid) * kStagePPitch;
+    }
+    __syncwarp();  // lanes 1-31 wait here for lane 0: the block-wide barrier below must be reached by whole warps
+  } else if (warp == kMmaWarp) {
+    // =================================================== MMA issuer =====================================================
+    if (lane == 0) {
+      auto wait = [&](uint32_t b, uint32_t parity) {
+        if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
+      };
+      const uint32_t idesc_s = instr_desc(128, 128, 1, 0, 0);
+      const uint32_t idesc_p2c = instr_desc(128, 32, 1, 0, 0);
+      const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
+      BufState bs;
+      int pv_seen = 0;   // P.V completions observed so far, in order
+      int band_idx = 0;
+      auto wait_pv_done = [&](int upto) {  // every P.V up to tile `upto` has finished
+        while (ok && pv_seen <= upto) { wait(bar(kBarO), uint32_t(pv_seen) & 1u); ++pv_seen; }
+      };
+      // scores (and position products) of tile j; returns the S buffer through `buf`
+      auto issue_scores = [&](int j, int& buf, uint32_t& parity) {
+        const int kind = tile_kind(j);
+        const int s = j & 1;
+        const uint32_t kq = smem + kSmemQ, kk = smem + kSmemK + s * 16384;
+        bs.next(kind == kBand, buf, parity);
+        if (kind == kBand) {
+          if (j > 0) wait_pv_done(j - 1);  // S buffers, the product area and the c2p stage are all free
+          wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
+          wait(bar(kBarWin), uint32_t(band_idx) & 1u);
+          tc_fence_after();
+          if (ok && has_c2p) {
+            // c2pT[p][m] = X_k[p].Q[m]: two 128-position blocks -> product columns [0,128) and [128,256)
 #pragma unroll 1
-        for (int c8 = 0; c8 < 8; ++c8) {
-          uint32_t r[32];
-          tmem_ld32(tmem_lane + kColBias + c8 * 32, r);
-          tmem_wait_ld();
+            for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-            sts_v4(row_addr + (c8 * 4 + q4) * 16,
-                   pack_bf16x2(__uint_as_float(r[q4 * 8 + 0]), __uint_as_float(r[q4 * 8 + 1])),
-                   pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]), __uint_as_float(r[q4 * 8 + 3])),
-                   pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]), __uint_as_float(r[q4 * 8 + 5])),
-                   pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]), __uint_as_float(r[q4 * 8 + 7])));
-        }
-      }
-      tc_fence_before();
-      sync_check();
-      if (tid == 0 && ok) {
-        tc_fence_after();
-        if (has_c2p) {
-          // c2pT[j][m] = X_k[j].Q[m]   two 128-row blocks of the window -> columns [0,128) and [128,256) of the bias area
+              for (int ks = 0; ks < 4; ++ks)
+                mma_bf16(tmem_base + kColR + blk * 128,
+                         smem_desc_sw128(smem + kSmemWinK + blk * 16384 + ks * 32, 1024, 16),
+                         smem_desc_sw128(kq + ks * 32, 1024, 16), idesc_s, ks > 0);
+          }
+          mma_commit(bar(kBarR));
+          wait(bar(kBarRFree), uint32_t(band_idx) & 1u);  // the softmax groups have drained the c2p product
+          tc_fence_after();
+          if (ok && has_p2c) {
+            // product (b, t) = X_q[32(3-b+t) .. +128) . K[32b .. +32)^T  -> 32 columns at R + 32(2b+t)
+#pragma unroll 1
+            for (int b = 0; b < 4; ++b)
+#pragma unroll 1
+              for (int t = 0; t < 2; ++t)
 #pragma unroll
-          for (int blk = 0; blk < 2; ++blk)
+                for (int ks = 0; ks < 4; ++ks)
+                  mma_bf16(tmem_base + kColR + 32 * (2 * b + t),
+                           smem_desc_sw128(smem + kSmemWinQ + 4096 * (3 - b + t) + ks * 32, 1024, 16),
+                           smem_desc_sw128(kk + 4096 * b + ks * 32, 1024, 16), idesc_p2c, ks > 0);
+          }
+          if (ok) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmem_base + kColBias + blk * 128,
-                       smem_desc_sw128(smem + kSmemWinK + blk * 16384 + ks * 32, 1024, 16),
-                       smem_desc_sw128(smem + kSmemQ + ks * 32, 1024, 16), idesc_s, ks > 0);
-        }
+              mma_bf16(tmem_base + sbuf_col(buf), smem_desc_sw128(kq + ks * 32, 1024, 16),
+                       smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, ks > 0);
+          }
+          mma_commit(bar(kBarS + buf));
+          mma_commit(bar(kBarKFree + s));
+          mma_commit(bar(kBarWinFree));
+          ++band_idx;
+        } else {
+          // the buffer's previous tenant was tile j-2 (or earlier): its P must have been consumed
+          if (j >= 2) wait_pv_done(j - 2);
+          wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
+          tc_fence_after();
+          if (ok) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_bf16(tmem_base + kColS, smem_desc_sw128(smem + kSmemQ + ks * 32, 1024, 16),
-                   smem_desc_sw128(smem + kSmemK + ks * 32, 1024, 16), idesc_s, ks > 0);
-        mma_commit(bar_s);
+            for (int ks = 0; ks < 4; ++ks)
+              mma_bf16(tmem_base + sbuf_col(buf), smem_desc_sw128(kq + ks * 32, 1024, 16),
+                       smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, ks > 0);
+            if (has_p2c && kind != kPlain) {
+              const uint32_t sat = smem + kSmemSat + (kind == kSatHi ? 0u : 1024u);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)  // every 8-row group of the operand is the same 8 rows: group stride 0
+                mma_bf16(tmem_base + sbuf_col(buf), smem_desc_sw128(sat + ks * 32, 0, 16),
+                         smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, 1);
+            }
+          }
+          mma_commit(bar(kBarS + buf));
+          mma_commit(bar(kBarKFree + s));
+        }
+      };
+
+      wait(bar(kBarQ), 0);
+      int buf_cur = 0, buf_nxt = 0;
+      uint32_t par_cur = 0, par_nxt = 0;
+      bool nxt_issued = false;
+      issue_scores(0, buf_cur, par_cur);
+      for (int j = 0; j < num_kt; ++j) {
+        nxt_issued = false;
+        if (j + 1 < num_kt && tile_kind(j) != kBand && tile_kind(j + 1) != kBand) {
+          issue_scores(j + 1, buf_nxt, par_nxt);  // overlaps the softmax of tile j
+          nxt_issued = true;
+        }
+        // O += P.V once both groups have written P over their S columns
+        wait(bar(kBarP + buf_cur), par_cur);
+        // P.V of the tile before finished long ago; observing it here, every tile, keeps this thread at most one phase
+        // behind the barrier (a parity wait cannot tell a phase from the one two later)
+        if (j > 0) wait_pv_done(j - 1);
+        wait(bar(kBarV + (j & 1)), uint32_t(j >> 1) & 1u);
+        tc_fence_after();
+        if (ok) {
+          const uint32_t vv = smem + kSmemV + (j & 1) * 16384;
+#pragma unroll 2
+          for (int ks = 0; ks < 8; ++ks)
+            mma_bf16_ts(tmem_base + kColO, tmem_base + sbuf_col(buf_cur) + 64 * (ks >> 2) + 8 * (ks & 3),
+                        smem_desc_sw128(vv + ks * 2048, 1024, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        mma_commit(bar(kBarO));
+        mma_commit(bar(kBarVFree + (j & 1)));
+        if (j + 1 < num_kt && !nxt_issued) issue_scores(j + 1, buf_nxt, par_nxt);
+        buf_cur = buf_nxt; par_cur = par_nxt;
       }
-      wait_all(bar_s, ph_s); ph_s ^= 1;
-      tc_fence_after();
-      if (has_c2p && ok) {
-#pragma unroll 1
-        for (int blk = 0; blk < 2; ++blk) {
-          const uint32_t row_addr = smem + kSmemStageC + uint32_t(blk * 128 + tid) * kStageCPitch;
+    }
+    __syncwarp();  // as above
+  }
+  } else {
+    reg_alloc<kSoftmaxRegs>();
+    // =================================================== softmax groups =================================================
+    const int g = warp >> 2;                 // key half
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;          // row of the tile
+    const uint32_t tmem_lane = tmem_base + (uint32_t(quad * 32) << 16);
+    const int my_row = m0 + r;
+    auto wait = [&](uint32_t b, uint32_t parity) {  // warp-uniform result
+      const bool mine = ok && mbar_wait_abortable(b, parity, abort_flag);
+      const bool all = __all_sync(0xffffffffu, mine);
+      if (ok && !all) *abort_flag = 1u;
+      ok = all;
+    };
+
+    wait(bar(kBarQ), 0);
+    float rc_lo = 0.f, rc_hi = 0.f;  // saturated c2p terms of this row: Q[m].X_k[first row], Q[m].X_k[last row]
+    if (has_c2p && ok) {
+      const __nv_bfloat16* xk_h = args.xk + (int64_t)head * args.xrows * kHeadDim;
+      const uint32_t q_row = smem + kSmemQ + uint32_t(r) * 128u;
+      rc_lo = dot_q_row(q_row, r, xk_h);
+      rc_hi = dot_q_row(q_row, r, xk_h + (int64_t)(args.xrows - 1) * kHeadDim);
+    }
+
+    BufState bs;
+    uint32_t band_idx = 0;
+    float m_used = 0.f, l_run = 0.f;
+
+    for (int j = 0; j < num_kt; ++j) {
+      const int n0 = j * kTileN;
+      const int kind = tile_kind(j);
+      int buf; uint32_t parity;
+      bs.next(kind == kBand, buf, parity);
+
+      if (kind == kBand) {
+        // ---- drain this group's half of the c2p product to shared memory as bf16 [position][query row] ----
+        wait(bar(kBarR), band_idx & 1u);
+        tc_fence_after();
+        if (has_c2p && ok) {
+          const uint32_t row_addr = smem + kSmemStageC + uint32_t(g * 128 + r) * kStageCPitch;
 #pragma unroll 1
           for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t r[32];
-            tmem_ld32(tmem_lane + kColBias + blk * 128 + c4 * 32, r);
+            uint32_t t[32];
+            tmem_ld32(tmem_lane + kColR + g * 128 + c4 * 32, t);
             tmem_wait_ld();
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4)
               sts_v4(row_addr + (c4 * 4 + q4) * 16,
-                     pack_bf16x2(__uint_as_float(r[q4 * 8 + 0]), __uint_as_float(r[q4 * 8 + 1])),
-                     pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]), __uint_as_float(r[q4 * 8 + 3])),
-                     pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]), __uint_as_float(r[q4 * 8 + 5])),
-                     pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]), __uint_as_float(r[q4 * 8 + 7])));
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 0]), __uint_as_float(t[q4 * 8 + 1])),
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 2]), __uint_as_float(t[q4 * 8 + 3])),
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 4]), __uint_as_float(t[q4 * 8 + 5])),
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 6]), __uint_as_float(t[q4 * 8 + 7])));
           }
         }
+        tc_fence_before();
+        mbar_arrive(bar(kBarRFree));
+        ++band_idx;
+        bar_sync(1, kSoftmaxThreads);  // the whole stage is visible to both groups
       }
-      tc_fence_before();
-      sync_check();
-      sat_built = kPlain;  // the stage area overlays the saturated tile
-    } else {
-      // ---- plain or saturated tile pair -----------------------------------------------------------------------------
-      const bool want_sat = has_p2c && kind != kPlain;
-      wait_all(bar_pv, ph_pv ^ 1);  // previous P.V (if any) done: P is free, O may be rescaled
-      if (want_sat && sat_built != kind) {
-        // every row of the tile = the saturated pos_query row, in the 128-byte-swizzled operand layout
-        const __nv_bfloat16* src = args.xq + ((int64_t)head * args.xrows + (kind == kSatHi ? args.xrows - 1 : 0)) * kHeadDim;
-        const uint4* s4 = reinterpret_cast<const uint4*>(src);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = __ldg(s4 + c);
-          sts_v4(smem + kSmemSat + uint32_t(tid) * 128u + (uint32_t(c ^ (tid & 7)) << 4), v.x, v.y, v.z, v.w);
-        }
-        fence_proxy_async_smem();
-        sync_check();
-        sat_built = kind;
-      }
-      if (tid == 0 && ok) {
-        const bool ready = wait_one(bar_k, ph_k);
-        tc_fence_after();
-        if (ready) {
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_bf16(tmem_base + kColS, smem_desc_sw128(smem + kSmemQ + ks * 32, 1024, 16),
-                     smem_desc_sw128(smem + kSmemK + ks * 32, 1024, 16), idesc_s, ks > 0);
-          if (want_sat) {
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmem_base + kColS, smem_desc_sw128(smem + kSmemSat + ks * 32, 1024, 16),
-                       smem_desc_sw128(smem + kSmemK + ks * 32, 1024, 16), idesc_s, 1);
-          }
-        }
-        mma_commit(bar_s);
-      }
-      wait_all(bar_s, ph_s); ph_s ^= 1;
+
+      wait(bar(kBarS + buf), parity);
       tc_fence_after();
-    }
-    ph_k ^= 1;
 
-    // K is consumed: fetch the next key tile while the softmax runs
-    if (tid == 0 && ok && j + 1 < num_kt) {
-      mbar_expect_tx(bar_k, 16384);
-      tma_load_3d(smem + kSmemK, &args.tm_k, bar_k, 0, head, seq_row0 + n0 + kTileN);
-    }
+      // ---- this thread's 64 scores (+ p2c through the quadrant shuffle) ----
+      float s[64];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t a[32];
+        if (ok) tmem_ld32(tmem_lane + sbuf_col(buf) + 64 * g + 32 * ch, a);
+        if (kind == kBand && has_p2c) {
+          uint32_t t0[32], t1[32];
+          if (ok) {
+            tmem_ld32(tmem_lane + kColR + 32 * (2 * (2 * g + ch)), t0);
+            tmem_ld32(tmem_lane + kColR + 32 * (2 * (2 * g + ch) + 1), t1);
+            tmem_wait_ld();
+          }
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const uint32_t x = (lane + c <= 30) ? t1[c] : t0[c];
+            const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - c) & 31);
+            s[32 * ch + c] = __uint_as_float(a[c]) + __uint_as_float(y);
+          }
+        } else {
+          if (ok) tmem_wait_ld();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) s[32 * ch + c] = __uint_as_float(a[c]);
+        }
+      }
+      float row_const = 0.f;
+      if (kind == kBand) {
+        if (has_c2p) {
+          // c2p[m][i] sits at stage[(m + 127 - i)][m]
+          const uint32_t base = smem + kSmemStageC + uint32_t(r + 127 - 64 * g) * kStageCPitch + uint32_t(r) * 2u;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) s[i] += bf16_bits_to_f32(lds_u16(base - uint32_t(i) * kStageCPitch));
+        }
+      } else if (kind == kSatHi) {
+        row_const = rc_hi;
+      } else if (kind == kSatLo) {
+        row_const = rc_lo;
+      }
+      if (n0 + kTileN > len) {  // keys past the end of the sequence
+        const int valid = len - n0 - 64 * g;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) s[i] = i < valid ? s[i] : -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+      // the two threads of a row agree on the row maximum
+      const uint32_t xch = smem + kSmemXchg + uint32_t(j & 1) * 1024u;
+      sts_f32(xch + uint32_t(g) * 512u + uint32_t(r) * 4u, mx);
+      bar_sync(1, kSoftmaxThreads);
+      mx = fmaxf(mx, lds_f32(xch + uint32_t(g ^ 1) * 512u + uint32_t(r) * 4u));
 
-    // ---- softmax on this thread's row -----------------------------------------------------------------------------------
-    float s[kTileN];
-    if (ok) {
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t r[32];
-        tmem_ld32(tmem_lane + kColS + c4 * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c4 * 32 + i] = __uint_as_float(r[i]);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < kTileN; ++i) s[i] = 0.f;
-    }
-    float row_const = 0.f;
-    if (kind == kBand) {
-      if (has_c2p) {
-        // c2p[m][n] sits at stage_c[(m + 127 - i)][m], i = n - n0
-        const uint32_t base = smem + kSmemStageC + uint32_t(tid + 127) * kStageCPitch + uint32_t(tid) * 2u;
-#pragma unroll
-        for (int i = 0; i < kTileN; ++i) s[i] += bf16_bits_to_f32(lds_u16(base - uint32_t(i) * kStageCPitch));
-      }
-      if (has_p2c) {
-        // p2c[m][n] sits at stage_p[i][(m + 127 - i)]
-        const uint32_t base = smem + kSmemStageP + uint32_t(tid + 127) * 2u;
-#pragma unroll
-        for (int i = 0; i < kTileN; ++i) s[i] += bf16_bits_to_f32(lds_u16(base + uint32_t(i) * (kStagePPitch - 2u)));
-      }
-    } else if (kind == kSatHi) {
-      row_const = rc_hi;
-    } else if (kind == kSatLo) {
-      row_const = rc_lo;
-    }
-    if (n0 + kTileN > len) {  // keys past the end of the sequence
-      const int valid = len - n0;
-#pragma unroll
-      for (int i = 0; i < kTileN; ++i) s[i] = i < valid ? s[i] : -INFINITY;
-    }
-    float mx = s[0];
-#pragma unroll
-    for (int i = 1; i < kTileN; ++i) mx = fmaxf(mx, s[i]);
-    const float t_max = (mx + row_const) * args.scale_log2;
-    if (j == 0) {
-      m_used = t_max;
-    } else {
-      const bool need = t_max > m_used + 8.f;
-      if (__any_sync(0xffffffffu, need)) {  // warp-uniform: O of these 32 rows is rescaled in TMEM
-        const float m_new = fmaxf(m_used, t_max);
-        const float alpha = ex2(m_used - m_new);
-        l_run *= alpha;
-        m_used = m_new;
-        if (ok) {
-#pragma unroll
-          for (int c2 = 0; c2 < 2; ++c2) {
-            uint32_t r[32];
-            tmem_ld32(tmem_lane + kColO + c2 * 32, r);
+      const float t_max = (mx + row_const) * args.scale_log2;
+      if (j == 0) {
+        m_used = t_max;
+      } else {
+        // The previous P.V has finished writing O.  Observed on every tile (it is long done by now) so that this thread
+        // never falls two phases behind the barrier, which a parity wait could not tell apart.
+        wait(bar(kBarO), uint32_t(j - 1) & 1u);
+        tc_fence_after();
+        const bool need = t_max > m_used + 8.f;
+        if (__any_sync(0xffffffffu, need)) {  // warp-uniform, and the same in both groups: rescale O of these 32 rows
+          const float m_new = fmaxf(m_used, t_max);
+          const float alpha = ex2(m_used - m_new);
+          l_run *= alpha;
+          m_used = m_new;
+          if (ok) {
+            uint32_t o[32];
+            tmem_ld32(tmem_lane + kColO + 32 * g, o);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tmem_lane + kColO + c2 * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tmem_lane + kColO + 32 * g, o);
+            tmem_wait_st();
           }
-          tmem_wait_st();
         }
       }
-    }
-    const float off = row_const * args.scale_log2 - m_used;
-    float l_add = 0.f;
+      const float off = row_const * args.scale_log2 - m_used;
+      float l_add = 0.f;
 #pragma unroll
-    for (int i = 0; i < kTileN; ++i) {
-      s[i] = ex2(fmaf(s[i], args.scale_log2, off));
-      l_add += s[i];
-    }
-    l_run += l_add;
-    // P as the bf16 A operand of P.V: two 64-key halves, 128-byte rows, 16-byte chunks XOR-swizzled by (row & 7)
-#pragma unroll
-    for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int b = kb * 64 + c * 8;
-        sts_v4(smem + kSmemP + kb * 16384 + uint32_t(tid) * 128u + (uint32_t(c ^ (tid & 7)) << 4),
-               pack_bf16x2(s[b + 0], s[b + 1]), pack_bf16x2(s[b + 2], s[b + 3]), pack_bf16x2(s[b + 4], s[b + 5]),
-               pack_bf16x2(s[b + 6], s[b + 7]));
+      for (int i = 0; i < 64; ++i) {
+        s[i] = ex2(fmaf(s[i], args.scale_log2, off));
+        l_add += s[i];
       }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    sync_check();
+      l_run += l_add;
+      // P as bf16 pairs over this group's own S columns (first 32 of its 64)
+      if (ok) {
+        uint32_t p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) p[i] = pack_bf16x2(s[2 * i], s[2 * i + 1]);
+        tmem_st32(tmem_lane + sbuf_col(buf) + 64 * g, p);
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      mbar_arrive(bar(kBarP + buf));
+    }
 
-    // ---- O += P.V ------------------------------------------------------------------------------------------------------------
-    if (tid == 0 && ok) {
-      const bool ready = wait_one(bar_v, ph_v);
-      tc_fence_after();
-      if (ready) {
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          mma_bf16(tmem_base + kColO,
-                   smem_desc_sw128(smem + kSmemP + (ks >> 2) * 16384 + (ks & 3) * 32, 1024, 16),
-                   smem_desc_sw128(smem + kSmemV + ks * 2048, 1024, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-      }
-      mma_commit(bar_pv);
-    }
-    ph_v ^= 1;
-    ph_pv ^= 1;
-    if (j + 1 < num_kt) {
-      // V may only be overwritten once this P.V has read it
-      if (tid == 0 && ok) {
-        wait_one(bar_pv, ph_pv ^ 1);
-        mbar_expect_tx(bar_v, 16384);
-        tma_load_3d(smem + kSmemV, &args.tm_v, bar_v, 0, head, seq_row0 + n0 + kTileN);
-      }
-    }
-  }
-
-  // ---- epilogue -------------------------------------------------------------------------------------------------------------
-  wait_all(bar_pv, ph_pv ^ 1);
-  tc_fence_after();
-  if (ok) {
-    const bool valid = my_row < len;
-    const bool pad = !valid && my_row < row_limit;  // dense padding rows inside a partly valid tile get zeros
-    const float inv = valid ? 1.f / l_run : 0.f;
-    uint4* o4 = reinterpret_cast<uint4*>(out_ptr);
-#pragma unroll
-    for (int c2 = 0; c2 < 2; ++c2) {
-      uint32_t r[32];
-      tmem_ld32(tmem_lane + kColO + c2 * 32, r);  // whole warps execute this, whatever their rows
+    // ---- epilogue: combine the two row sums, O / l, write this group's 32 output columns ----
+    sts_f32(smem + kSmemLsum + uint32_t(g) * 512u + uint32_t(r) * 4u, l_run);
+    bar_sync(1, kSoftmaxThreads);
+    const float l_tot = l_run + lds_f32(smem + kSmemLsum + uint32_t(g ^ 1) * 512u + uint32_t(r) * 4u);
+    wait(bar(kBarO), uint32_t(num_kt - 1) & 1u);
+    tc_fence_after();
+    if (ok) {
+      const bool valid = my_row < len;
+      const bool pad = !valid && my_row < row_limit;  // dense padding rows inside a partly valid tile get zeros
+      const float inv = valid ? 1.f / l_tot : 0.f;
+      uint32_t o[32];
+      tmem_ld32(tmem_lane + kColO + 32 * g, o);  // whole warps execute this, whatever their rows
       tmem_wait_ld();
       if (valid || pad) {
+        uint4* o4 = reinterpret_cast<uint4*>(args.out + (int64_t)(seq_row0 + my_row) * args.o_rs +
+                                             (int64_t)head * args.o_hs + 32 * g);
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           uint4 v = make_uint4(0, 0, 0, 0);
           if (valid)
-            v = make_uint4(pack_bf16x2(__uint_as_float(r[q4 * 8 + 0]) * inv, __uint_as_float(r[q4 * 8 + 1]) * inv),
-                           pack_bf16x2(__uint_as_float(r[q4 * 8 + 2]) * inv, __uint_as_float(r[q4 * 8 + 3]) * inv),
-                           pack_bf16x2(__uint_as_float(r[q4 * 8 + 4]) * inv, __uint_as_float(r[q4 * 8 + 5]) * inv),
-                           pack_bf16x2(__uint_as_float(r[q4 * 8 + 6]) * inv, __uint_as_float(r[q4 * 8 + 7]) * inv));
-          o4[c2 * 4 + q4] = v;
+            v = make_uint4(pack_bf16x2(__uint_as_float(o[q4 * 8 + 0]) * inv, __uint_as_float(o[q4 * 8 + 1]) * inv),
+                           pack_bf16x2(__uint_as_float(o[q4 * 8 + 2]) * inv, __uint_as_float(o[q4 * 8 + 3]) * inv),
+                           pack_bf16x2(__uint_as_float(o[q4 * 8 + 4]) * inv, __uint_as_float(o[q4 * 8 + 5]) * inv),
+                           pack_bf16x2(__uint_as_float(o[q4 * 8 + 6]) * inv, __uint_as_float(o[q4 * 8 + 7]) * inv));
+          o4[q4] = v;
         }
+        if (g == 0 && args.lse != nullptr)
+          args.lse[(int64_t)(seq_row0 + my_row) * args.heads + head] =
+              valid ? (m_used + log2f(l_tot)) * 0.6931471805599453f : 0.f;
       }
     }
-    if (args.lse != nullptr && (valid || pad))
-      args.lse[(int64_t)(seq_row0 + my_row) * args.heads + head] =
-          valid ? (m_used + log2f(l_run)) * 0.6931471805599453f : 0.f;
   }
+
+  // ---- teardown -------------------------------------------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (!ok || *abort_flag != 0u) {
+  if (*abort_flag != 0u) {
     if (tid == 0 && args.status != nullptr) atomicOr(reinterpret_cast<unsigned int*>(args.status), FDB_DEV_TIMEOUT);
     // give copies and MMAs that may still be in flight a bounded time to land before TMEM and shared memory go away
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 0) tmem_dealloc(tmem_base, kTmemCols);
-}
-
-// ---- host side: tensor maps and launch ---------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// (rows, heads, 64) tensor with element strides -> 3-D map (d, head, row), box 64 x 1 x box_rows, 128-byte swizzle
-int make_map_rows(CUtensorMap* m, const void* base, int64_t rows, int heads, int64_t row_stride, int64_t head_stride,
-                  int box_rows, const char* what) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t dims[3] = {64, (cuuint64_t)heads, (cuuint64_t)rows};
-  const cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)row_stride * 2};
-  const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
-  return FDB_OK;
-}
-
-// expanded table (heads, xrows, 64) contiguous -> 3-D map (d, row, head), box 64 x 256 x 1
-int make_map_table(CUtensorMap* m, const void* base, int xrows, int heads, const char* what) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t dims[3] = {64, (cuuint64_t)xrows, (cuuint64_t)heads};
-  const cuuint64_t strides[2] = {128, (cuuint64_t)xrows * 128};
-  const cuuint32_t box[3] = {64, (cuuint32_t)kWindow, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
-  return FDB_OK;
+  if (warp == kMmaWarp) tmem_dealloc(tmem_base, kTmemCols);
 }
 
 }  // namespace
 
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream) {
+  const char* which = std::getenv("FDB_ATTN_KERNEL");
+  if (which != nullptr && std::strcmp(which, "serial") == 0) return launch_attn_fwd_serial(p, g, w, stream);
   if (p.dtype != FDB_BF16) return fail(FDB_ERR_UNSUPPORTED, "fused kernel: dtype %d is not built yet", p.dtype);
   FwdArgs a;
   char* ws = static_cast<char*>(p.workspace);
@@ -579,10 +611,8 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   if (slots <= 0) return FDB_OK;
   if (slots > 2147483647LL || p.heads > 65535) return fail(FDB_ERR_LIMIT, "grid too large");
 
-
   cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-
   attn_fwd_kernel<<<dim3((unsigned)slots, p.heads), kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "attn_fwd launch: %s", cudaGetErrorString(e));

@@ -31,8 +31,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait that also gives up as soon as another thread of the CTA has raised `*abort_flag`.
+__device__ __forceinline__ bool mbar_wait_abortable_slow(uint32_t bar, uint32_t parity, const volatile uint32_t* abort_flag) {
+  const long long t0 = clock64();
+#pragma unroll 1
+  for (uint32_t i = 0; i < (1u << 30); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag != 0u) return false;
+      if (clock64() - t0 > 4000000000LL) break;
+    }
+  }
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity, const volatile uint32_t* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 32; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_abortable_slow(bar, parity, abort_flag);
+}
+// Named barrier among `count` threads (count a multiple of 32); id 0 is __syncthreads.
+__device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 // Bounded wait: gives up after about two seconds of SM clock and reports false.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity) {
   const long long t0 = clock64();
 #pragma unroll 1
   for (uint32_t i = 0; i < (1u << 30); ++i) {
@@ -124,6 +150,15 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// A operand read from tensor memory (16-bit elements packed two per 32-bit column, row = lane), B from shared memory.
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on an mbarrier once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -155,6 +190,10 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- register reallocation between warpgroups (all four warps of a warpgroup execute it) --------------------------
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // ---- small math -------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {
