@@ -4,17 +4,20 @@
 // src/flashdeberta/ops/flash_attention_varlen.py:85-225) and the two bias GEMMs in front of them
 // (src/flashdeberta/model.py:189-192, :210-214).
 //
-// One CTA = one 128-row query tile of one (sequence, head); 12 warps (registers move from the producer warpgroup to the
-// softmax warpgroups with setmaxnreg):
-//   warps 0-3  softmax group 0: thread r owns row r of the tile, keys   0..63  of every 128-key tile
-//   warps 4-7  softmax group 1: thread r owns row r of the tile, keys  64..127
-//   warp  8    lane 0 issues every tcgen05.mma (and allocates tensor memory)
-//   warp  9    lane 0 issues every TMA load: Q once, K/V double-buffered, position-table windows
-// Per key tile:  S = Q.K^T  (tensor core, fp32 in TMEM)  ->  the two groups read their halves of S with tcgen05.ld, add the
-// position terms, agree on the row maximum through shared memory, write P = exp2(...) as bf16 back into tensor memory over
-// their own S columns  ->  O += P.V with P read from tensor memory and V from shared memory.  S is double-buffered, so the
-// scores of tile j+1 are computed while the softmax of tile j runs.  O stays in TMEM and is rescaled only when the running
-// maximum moved by more than 2^8.
+// One CTA = one 128-row query tile of one (sequence, head); 16 warps in four warpgroups (registers move from the
+// producer and drain groups to the softmax groups with setmaxnreg):
+//   warps 0-3   softmax group 0: thread r owns row r of the tile, keys   0..63  of every 128-key tile
+//   warps 4-7   softmax group 1: thread r owns row r of the tile, keys  64..127
+//   warp  8     lane 0 issues every tcgen05.mma (and the warp allocates tensor memory)
+//   warp  9     lane 0 issues every TMA load: Q once, K/V double-buffered, position-table windows
+//   warps 12-15 drain group: moves the c2p product of a band tile from tensor memory to shared memory (bf16)
+// Tensor memory (512 columns): O 64 | P 64 | S 128 | R 256 (position products of a band tile).
+//
+// Per key tile j:  S = Q.K^T (tensor core, fp32 in TMEM)  ->  both softmax groups pull their half of S (and of the p2c
+// product) into registers and release S and R at once, so the tensor core computes the scores of tile j+1 while the
+// softmax of tile j runs  ->  the groups agree on the row maximum through shared memory, write P = exp2(...) as bf16 pairs
+// into the P columns  ->  O += P.V with P read from tensor memory and V from shared memory.  O stays in TMEM and is
+// rescaled only when the running maximum moved by more than 2^8.
 //
 // Position terms (tables arrive expanded through the bucket function, see attn_prepare.cu; row of (m, n) is (m-n)-d_first):
 //   * saturated tile pair (all distances beyond a saturation point): c2p is one dot product per query row, folded into the
@@ -23,8 +26,9 @@
 //   * band tile pair: p2c comes from eight 128x32 products X_q[32(3-b+t) ..].K[32b ..]^T, b = key block, t = 0/1, arranged so
 //     that the value thread (quadrant w, lane l) needs for key 32b+c sits in its own quadrant at lane (l+31-c)&31 of product
 //     t = (l > c): one select on the source side and one warp shuffle per score element, fp32, no shared memory;
-//     c2p needs a transpose: X_k[window].Q^T (256x128) is drained from TMEM to shared memory as bf16 [position][query] and
-//     thread m reads c2p[m][m+127-i] at compile-time offsets from a per-thread base.
+//     c2p needs a transpose: X_k[window].Q^T (256x128) is computed into R ahead of the p2c product, the drain group writes it
+//     to shared memory as bf16 [position][query] while the softmax of the previous tile is still running, and thread m
+//     reads c2p[m][m+127-i] at compile-time offsets from a per-thread base.
 // No (rows x 2*span) bias tensor is ever written to global memory.
 //
 // Every mbarrier wait is bounded and gives up early once another role has raised the abort flag; the CTA then sets
@@ -47,15 +51,16 @@ namespace {
 using namespace ptx;
 
 constexpr int kSoftmaxThreads = 256;
-constexpr int kThreads = 384;           // three warpgroups: two softmax groups and one producer group (warps 10, 11 idle)
-constexpr int kMmaWarp = 8, kTmaWarp = 9;
-constexpr int kProducerRegs = 56, kSoftmaxRegs = 224;  // 168 * 384 = 40 * 128 + 232 * 256
+constexpr int kDrainThreads = 128;
+constexpr int kThreads = 512;            // four warpgroups: softmax 0, softmax 1, producers (warps 10, 11 idle), drain
+constexpr int kMmaWarp = 8, kTmaWarp = 9, kDrainWarp0 = 12;
+// 128 registers per thread at launch; after setmaxnreg: 40 * 128 + 72 * 128 + 200 * 256 = 65536
+constexpr int kProducerRegs = 40, kDrainRegs = 72, kSoftmaxRegs = 200;
 constexpr uint32_t kTmemCols = 512;
-// TMEM columns: O 64 | R 256 (position products of a band tile; its upper half doubles as S buffer 1) | S buffer 0
-constexpr uint32_t kColO = 0;
-constexpr uint32_t kColR = 64;
-constexpr uint32_t kColS1 = 192;
-constexpr uint32_t kColS0 = 320;
+constexpr uint32_t kColO = 0;     // 64 columns: output accumulator
+constexpr uint32_t kColP = 64;    // 64 columns: P as bf16 pairs (keys 0..63 in the first 32, keys 64..127 in the last 32)
+constexpr uint32_t kColS = 128;   // 128 columns: scores
+constexpr uint32_t kColR = 256;   // 256 columns: position products of a band tile
 
 // shared memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kSmemQ = 0;                      // 128 x 128 B
@@ -73,9 +78,23 @@ constexpr uint32_t kSmemBytes = kSmemBars + 256 + 1024;  // + alignment slack
 static_assert(kSmemSat == 217088, "shared memory map");
 static_assert(kSmemBytes <= 232448, "exceeds 227 KB");
 
+// mbarriers.  "count" = arrivals per phase.
 enum Bar : uint32_t {
-  kBarQ = 0, kBarK = 1, kBarV = 3, kBarKFree = 5, kBarVFree = 7, kBarWin = 9, kBarWinFree = 10, kBarS = 11, kBarP = 13,
-  kBarO = 15, kBarR = 16, kBarRFree = 17, kNumBars = 18
+  kBarQ = 0,         // 1   Q landed (TMA)
+  kBarK = 1,         // 1   K stage s landed (TMA), 2 stages
+  kBarV = 3,         // 1   V stage s landed (TMA), 2 stages
+  kBarKFree = 5,     // 1   the MMAs that read K stage s finished (tcgen05.commit)
+  kBarVFree = 7,     // 1   the P.V that read V stage s finished
+  kBarWin = 9,       // 1   position windows landed (TMA)
+  kBarWinFree = 10,  // 1   the MMAs that read the windows finished
+  kBarS = 11,        // 1   S (and the p2c product) of a tile are in tensor memory
+  kBarSFree = 12,    // 256 both softmax groups hold their scores in registers: S and R may be overwritten
+  kBarP = 13,        // 256 P of a tile is in tensor memory
+  kBarO = 14,        // 1   P.V of a tile finished
+  kBarC2p = 15,      // 1   the c2p product of a band tile is in R
+  kBarStage = 16,    // 128 the drain group has written the c2p stage (R may be overwritten, the stage may be read)
+  kBarGather = 17,   // 256 both softmax groups are done reading the c2p stage
+  kNumBars = 18
 };
 
 struct alignas(64) FwdArgs {
@@ -136,18 +155,6 @@ __device__ __forceinline__ float dot_q_row(uint32_t q_row_addr, int row, const _
   return acc;
 }
 
-// Which S buffer a tile uses and the parity of that buffer's barriers for this use.  Band tiles always take buffer 0
-// (buffer 1 lies inside the position-product area).  Every role walks the tiles in order with its own copy.
-struct BufState {
-  int cur = 0;
-  uint32_t uses[2] = {0u, 0u};
-  __device__ __forceinline__ void next(bool band, int& buf, uint32_t& parity) {
-    if (band) { buf = 0; cur = 1; } else { buf = cur; cur ^= 1; }
-    parity = uses[buf] & 1u;
-    ++uses[buf];
-  }
-};
-
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_constant__ FwdArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -197,7 +204,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   if (tid == 0) {
     *abort_flag = 0u;
     for (uint32_t i = 0; i < kNumBars; ++i) {
-      const uint32_t count = (i == kBarP || i == kBarP + 1 || i == kBarRFree) ? kSoftmaxThreads : 1u;
+      uint32_t count = 1u;
+      if (i == kBarSFree || i == kBarP || i == kBarGather) count = kSoftmaxThreads;
+      if (i == kBarStage) count = kDrainThreads;
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
@@ -218,165 +227,179 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 8u * kNumBars);
-  auto sbuf_col = [&](int b) -> uint32_t { return b == 0 ? kColS0 : kColS1; };
 
   bool ok = true;
 
-  if (warp >= kMmaWarp) {
-  reg_dealloc<kProducerRegs>();
-  if (warp == kTmaWarp) {
-    // =================================================== TMA producer ===================================================
-    if (lane == 0) {
-      auto wait = [&](uint32_t b, uint32_t parity) {
-        if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
-      };
-      tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
-      mbar_expect_tx(bar(kBarQ), 16384);
-      tma_load_3d(smem + kSmemQ, &args.tm_q, bar(kBarQ), 0, head, seq_row0 + m0);
-      int band_idx = 0;
-      for (int j = 0; j < num_kt; ++j) {
-        const int s = j & 1;
-        const uint32_t use = uint32_t(j >> 1);  // how often this stage was used before
-        if (j >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
-        if (!ok) break;
-        mbar_expect_tx(bar(kBarK + s), 16384);
-        tma_load_3d(smem + kSmemK + s * 16384, &args.tm_k, bar(kBarK + s), 0, head, seq_row0 + j * kTileN);
-        if (tile_kind(j) == kBand) {
-          if (band_idx > 0) wait(bar(kBarWinFree), uint32_t(band_idx - 1) & 1u);
-          if (!ok) break;
-          const int u0 = m0 - j * kTileN - (kTileN - 1) - args.d_first;
-          mbar_expect_tx(bar(kBarWin), (has_c2p ? 32768u : 0u) + (has_p2c ? 32768u : 0u));
-          if (has_c2p) tma_load_3d(smem + kSmemWinK, &args.tm_xk, bar(kBarWin), 0, u0, head);
-          if (has_p2c) tma_load_3d(smem + kSmemWinQ, &args.tm_xq, bar(kBarWin), 0, u0, head);
-          ++band_idx;
-        }
-        if (j >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
-        if (!ok) break;
-        mbar_expect_tx(bar(kBarV + s), 16384);
-        tma_load_3d(smem + kSmemV + s * 16384, &args.tm_v, bar(kBarV + s), 0, head, seq_row0 + j * kTileN);
-      }
-    }
-    __syncwarp();  // lanes 1-31 wait here for lane 0: the block-wide barrier below must be reached by whole warps
-  } else if (warp == kMmaWarp) {
-    // =================================================== MMA issuer =====================================================
-    if (lane == 0) {
-      auto wait = [&](uint32_t b, uint32_t parity) {
-        if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
-      };
-      const uint32_t idesc_s = instr_desc(128, 128, 1, 0, 0);
-      const uint32_t idesc_p2c = instr_desc(128, 32, 1, 0, 0);
-      const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
-      BufState bs;
-      int pv_seen = 0;   // P.V completions observed so far, in order
-      int band_idx = 0;
-      auto wait_pv_done = [&](int upto) {  // every P.V up to tile `upto` has finished
-        while (ok && pv_seen <= upto) { wait(bar(kBarO), uint32_t(pv_seen) & 1u); ++pv_seen; }
-      };
-      // scores (and position products) of tile j; returns the S buffer through `buf`
-      auto issue_scores = [&](int j, int& buf, uint32_t& parity) {
-        const int kind = tile_kind(j);
-        const int s = j & 1;
-        const uint32_t kq = smem + kSmemQ, kk = smem + kSmemK + s * 16384;
-        bs.next(kind == kBand, buf, parity);
-        if (kind == kBand) {
-          if (j > 0) wait_pv_done(j - 1);  // S buffers, the product area and the c2p stage are all free
-          wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
-          wait(bar(kBarWin), uint32_t(band_idx) & 1u);
-          tc_fence_after();
-          if (ok && has_c2p) {
-            // c2pT[p][m] = X_k[p].Q[m]: two 128-position blocks -> product columns [0,128) and [128,256)
+  if (warp >= kDrainWarp0) {
+    // =================================================== drain group ====================================================
+    reg_dealloc<kDrainRegs>();
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // TMEM lane = position row inside a 128-position block
+    const uint32_t tmem_lane = tmem_base + (uint32_t(quad * 32) << 16);
+    auto wait = [&](uint32_t b, uint32_t parity) {  // warp-uniform result
+      const bool mine = ok && mbar_wait_abortable(b, parity, abort_flag);
+      const bool all = __all_sync(0xffffffffu, mine);
+      if (ok && !all) *abort_flag = 1u;
+      ok = all;
+    };
+    uint32_t band_idx = 0;
+    for (int j = 0; j < num_kt; ++j) {
+      if (tile_kind(j) != kBand) continue;
+      wait(bar(kBarC2p), band_idx & 1u);                               // the product is in R
+      if (band_idx > 0) wait(bar(kBarGather), (band_idx - 1u) & 1u);   // nobody reads the previous stage any more
+      tc_fence_after();
+      if (has_c2p && ok) {
 #pragma unroll 1
-            for (int blk = 0; blk < 2; ++blk)
+        for (int blk = 0; blk < 2; ++blk) {
+          const uint32_t row_addr = smem + kSmemStageC + uint32_t(blk * 128 + r) * kStageCPitch;
+#pragma unroll 1
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t t[32];
+            tmem_ld32(tmem_lane + kColR + blk * 128 + c4 * 32, t);
+            tmem_wait_ld();
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                mma_bf16(tmem_base + kColR + blk * 128,
-                         smem_desc_sw128(smem + kSmemWinK + blk * 16384 + ks * 32, 1024, 16),
-                         smem_desc_sw128(kq + ks * 32, 1024, 16), idesc_s, ks > 0);
+            for (int q4 = 0; q4 < 4; ++q4)
+              sts_v4(row_addr + (c4 * 4 + q4) * 16,
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 0]), __uint_as_float(t[q4 * 8 + 1])),
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 2]), __uint_as_float(t[q4 * 8 + 3])),
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 4]), __uint_as_float(t[q4 * 8 + 5])),
+                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 6]), __uint_as_float(t[q4 * 8 + 7])));
           }
-          mma_commit(bar(kBarR));
-          wait(bar(kBarRFree), uint32_t(band_idx) & 1u);  // the softmax groups have drained the c2p product
-          tc_fence_after();
-          if (ok && has_p2c) {
-            // product (b, t) = X_q[32(3-b+t) .. +128) . K[32b .. +32)^T  -> 32 columns at R + 32(2b+t)
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar(kBarStage));
+      ++band_idx;
+    }
+  } else if (warp >= kMmaWarp) {
+    reg_dealloc<kProducerRegs>();
+    if (warp == kTmaWarp) {
+      // ================================================= TMA producer ===================================================
+      if (lane == 0) {
+        auto wait = [&](uint32_t b, uint32_t parity) {
+          if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
+        };
+        tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
+        mbar_expect_tx(bar(kBarQ), 16384);
+        tma_load_3d(smem + kSmemQ, &args.tm_q, bar(kBarQ), 0, head, seq_row0 + m0);
+        int band_idx = 0;
+        for (int j = 0; j < num_kt; ++j) {
+          const int s = j & 1;
+          const uint32_t use = uint32_t(j >> 1);  // how often this stage was used before
+          if (j >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
+          if (!ok) break;
+          mbar_expect_tx(bar(kBarK + s), 16384);
+          tma_load_3d(smem + kSmemK + s * 16384, &args.tm_k, bar(kBarK + s), 0, head, seq_row0 + j * kTileN);
+          if (tile_kind(j) == kBand) {
+            if (band_idx > 0) wait(bar(kBarWinFree), uint32_t(band_idx - 1) & 1u);
+            if (!ok) break;
+            const int u0 = m0 - j * kTileN - (kTileN - 1) - args.d_first;
+            mbar_expect_tx(bar(kBarWin), (has_c2p ? 32768u : 0u) + (has_p2c ? 32768u : 0u));
+            if (has_c2p) tma_load_3d(smem + kSmemWinK, &args.tm_xk, bar(kBarWin), 0, u0, head);
+            if (has_p2c) tma_load_3d(smem + kSmemWinQ, &args.tm_xq, bar(kBarWin), 0, u0, head);
+            ++band_idx;
+          }
+          if (j >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
+          if (!ok) break;
+          mbar_expect_tx(bar(kBarV + s), 16384);
+          tma_load_3d(smem + kSmemV + s * 16384, &args.tm_v, bar(kBarV + s), 0, head, seq_row0 + j * kTileN);
+        }
+      }
+      __syncwarp();  // lanes 1-31 wait here for lane 0: the block-wide barrier below must be reached by whole warps
+    } else if (warp == kMmaWarp) {
+      // ================================================= MMA issuer =====================================================
+      if (lane == 0) {
+        auto wait = [&](uint32_t b, uint32_t parity) {
+          if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
+        };
+        const uint32_t idesc_s = instr_desc(128, 128, 1, 0, 0);
+        const uint32_t idesc_p2c = instr_desc(128, 32, 1, 0, 0);
+        const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
+        int band_idx = 0;
+        // Scores (and position products) of tile j.  The caller has made sure S and R are free.
+        auto issue_scores = [&](int j) {
+          const int kind = tile_kind(j);
+          const int s = j & 1;
+          const uint32_t kq = smem + kSmemQ, kk = smem + kSmemK + s * 16384;
+          wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
+          if (kind == kBand) {
+            wait(bar(kBarWin), uint32_t(band_idx) & 1u);
+            tc_fence_after();
+            if (ok && has_c2p) {
+              // c2pT[p][m] = X_k[p].Q[m]: two 128-position blocks -> R columns [0,128) and [128,256)
 #pragma unroll 1
-            for (int b = 0; b < 4; ++b)
-#pragma unroll 1
-              for (int t = 0; t < 2; ++t)
+              for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
-                  mma_bf16(tmem_base + kColR + 32 * (2 * b + t),
-                           smem_desc_sw128(smem + kSmemWinQ + 4096 * (3 - b + t) + ks * 32, 1024, 16),
-                           smem_desc_sw128(kk + 4096 * b + ks * 32, 1024, 16), idesc_p2c, ks > 0);
+                  mma_bf16(tmem_base + kColR + blk * 128,
+                           smem_desc_sw128(smem + kSmemWinK + blk * 16384 + ks * 32, 1024, 16),
+                           smem_desc_sw128(kq + ks * 32, 1024, 16), idesc_s, ks > 0);
+            }
+            mma_commit(bar(kBarC2p));
+            wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
+            tc_fence_after();
+            if (ok && has_p2c) {
+              // product (b, t) = X_q[32(3-b+t) .. +128) . K[32b .. +32)^T  -> 32 columns at R + 32(2b+t)
+#pragma unroll 1
+              for (int b = 0; b < 4; ++b)
+#pragma unroll 1
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                  for (int ks = 0; ks < 4; ++ks)
+                    mma_bf16(tmem_base + kColR + 32 * (2 * b + t),
+                             smem_desc_sw128(smem + kSmemWinQ + 4096 * (3 - b + t) + ks * 32, 1024, 16),
+                             smem_desc_sw128(kk + 4096 * b + ks * 32, 1024, 16), idesc_p2c, ks > 0);
+            }
+            ++band_idx;
+          } else {
+            tc_fence_after();
           }
           if (ok) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmem_base + sbuf_col(buf), smem_desc_sw128(kq + ks * 32, 1024, 16),
+              mma_bf16(tmem_base + kColS, smem_desc_sw128(kq + ks * 32, 1024, 16),
                        smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, ks > 0);
-          }
-          mma_commit(bar(kBarS + buf));
-          mma_commit(bar(kBarKFree + s));
-          mma_commit(bar(kBarWinFree));
-          ++band_idx;
-        } else {
-          // the buffer's previous tenant was tile j-2 (or earlier): its P must have been consumed
-          if (j >= 2) wait_pv_done(j - 2);
-          wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
-          tc_fence_after();
-          if (ok) {
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmem_base + sbuf_col(buf), smem_desc_sw128(kq + ks * 32, 1024, 16),
-                       smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, ks > 0);
-            if (has_p2c && kind != kPlain) {
+            if (has_p2c && (kind == kSatHi || kind == kSatLo)) {
               const uint32_t sat = smem + kSmemSat + (kind == kSatHi ? 0u : 1024u);
 #pragma unroll
               for (int ks = 0; ks < 4; ++ks)  // every 8-row group of the operand is the same 8 rows: group stride 0
-                mma_bf16(tmem_base + sbuf_col(buf), smem_desc_sw128(sat + ks * 32, 0, 16),
+                mma_bf16(tmem_base + kColS, smem_desc_sw128(sat + ks * 32, 0, 16),
                          smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, 1);
             }
           }
-          mma_commit(bar(kBarS + buf));
+          mma_commit(bar(kBarS));
           mma_commit(bar(kBarKFree + s));
-        }
-      };
+          if (kind == kBand) mma_commit(bar(kBarWinFree));
+        };
 
-      wait(bar(kBarQ), 0);
-      int buf_cur = 0, buf_nxt = 0;
-      uint32_t par_cur = 0, par_nxt = 0;
-      bool nxt_issued = false;
-      issue_scores(0, buf_cur, par_cur);
-      for (int j = 0; j < num_kt; ++j) {
-        nxt_issued = false;
-        if (j + 1 < num_kt && tile_kind(j) != kBand && tile_kind(j + 1) != kBand) {
-          issue_scores(j + 1, buf_nxt, par_nxt);  // overlaps the softmax of tile j
-          nxt_issued = true;
-        }
-        // O += P.V once both groups have written P over their S columns
-        wait(bar(kBarP + buf_cur), par_cur);
-        // P.V of the tile before finished long ago; observing it here, every tile, keeps this thread at most one phase
-        // behind the barrier (a parity wait cannot tell a phase from the one two later)
-        if (j > 0) wait_pv_done(j - 1);
-        wait(bar(kBarV + (j & 1)), uint32_t(j >> 1) & 1u);
-        tc_fence_after();
-        if (ok) {
-          const uint32_t vv = smem + kSmemV + (j & 1) * 16384;
+        wait(bar(kBarQ), 0);
+        issue_scores(0);
+        for (int j = 0; j < num_kt; ++j) {
+          if (j + 1 < num_kt) {
+            // as soon as both softmax groups hold tile j in registers, S and R are free: scores of tile j+1
+            wait(bar(kBarSFree), uint32_t(j) & 1u);
+            issue_scores(j + 1);
+          }
+          // O += P.V once both groups have written P
+          wait(bar(kBarP), uint32_t(j) & 1u);
+          wait(bar(kBarV + (j & 1)), uint32_t(j >> 1) & 1u);
+          tc_fence_after();
+          if (ok) {
+            const uint32_t vv = smem + kSmemV + (j & 1) * 16384;
 #pragma unroll 2
-          for (int ks = 0; ks < 8; ++ks)
-            mma_bf16_ts(tmem_base + kColO, tmem_base + sbuf_col(buf_cur) + 64 * (ks >> 2) + 8 * (ks & 3),
-                        smem_desc_sw128(vv + ks * 2048, 1024, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < 8; ++ks)
+              mma_bf16_ts(tmem_base + kColO, tmem_base + kColP + 8 * ks,
+                          smem_desc_sw128(vv + ks * 2048, 1024, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          mma_commit(bar(kBarO));
+          mma_commit(bar(kBarVFree + (j & 1)));
         }
-        mma_commit(bar(kBarO));
-        mma_commit(bar(kBarVFree + (j & 1)));
-        if (j + 1 < num_kt && !nxt_issued) issue_scores(j + 1, buf_nxt, par_nxt);
-        buf_cur = buf_nxt; par_cur = par_nxt;
       }
+      __syncwarp();  // as above
     }
-    __syncwarp();  // as above
-  }
   } else {
-    reg_alloc<kSoftmaxRegs>();
     // =================================================== softmax groups =================================================
+    reg_alloc<kSoftmaxRegs>();
     const int g = warp >> 2;                 // key half
     const int quad = warp & 3;
     const int r = quad * 32 + lane;          // row of the tile
@@ -398,51 +421,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       rc_hi = dot_q_row(q_row, r, xk_h + (int64_t)(args.xrows - 1) * kHeadDim);
     }
 
-    BufState bs;
     uint32_t band_idx = 0;
     float m_used = 0.f, l_run = 0.f;
 
     for (int j = 0; j < num_kt; ++j) {
       const int n0 = j * kTileN;
       const int kind = tile_kind(j);
-      int buf; uint32_t parity;
-      bs.next(kind == kBand, buf, parity);
 
-      if (kind == kBand) {
-        // ---- drain this group's half of the c2p product to shared memory as bf16 [position][query row] ----
-        wait(bar(kBarR), band_idx & 1u);
-        tc_fence_after();
-        if (has_c2p && ok) {
-          const uint32_t row_addr = smem + kSmemStageC + uint32_t(g * 128 + r) * kStageCPitch;
-#pragma unroll 1
-          for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t t[32];
-            tmem_ld32(tmem_lane + kColR + g * 128 + c4 * 32, t);
-            tmem_wait_ld();
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-              sts_v4(row_addr + (c4 * 4 + q4) * 16,
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 0]), __uint_as_float(t[q4 * 8 + 1])),
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 2]), __uint_as_float(t[q4 * 8 + 3])),
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 4]), __uint_as_float(t[q4 * 8 + 5])),
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 6]), __uint_as_float(t[q4 * 8 + 7])));
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(bar(kBarRFree));
-        ++band_idx;
-        bar_sync(1, kSoftmaxThreads);  // the whole stage is visible to both groups
-      }
-
-      wait(bar(kBarS + buf), parity);
+      wait(bar(kBarS), uint32_t(j) & 1u);
       tc_fence_after();
 
-      // ---- this thread's 64 scores (+ p2c through the quadrant shuffle) ----
+      // ---- this thread's 64 scores (+ p2c through the quadrant shuffle) into registers, then S and R are released ----
       float s[64];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t a[32];
-        if (ok) tmem_ld32(tmem_lane + sbuf_col(buf) + 64 * g + 32 * ch, a);
+        if (ok) tmem_ld32(tmem_lane + kColS + 64 * g + 32 * ch, a);
         if (kind == kBand && has_p2c) {
           uint32_t t0[32], t1[32];
           if (ok) {
@@ -462,14 +456,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           for (int c = 0; c < 32; ++c) s[32 * ch + c] = __uint_as_float(a[c]);
         }
       }
+      tc_fence_before();
+      mbar_arrive(bar(kBarSFree));
+
       float row_const = 0.f;
       if (kind == kBand) {
+        wait(bar(kBarStage), band_idx & 1u);  // the c2p stage of this tile is complete
         if (has_c2p) {
           // c2p[m][i] sits at stage[(m + 127 - i)][m]
           const uint32_t base = smem + kSmemStageC + uint32_t(r + 127 - 64 * g) * kStageCPitch + uint32_t(r) * 2u;
 #pragma unroll
           for (int i = 0; i < 64; ++i) s[i] += bf16_bits_to_f32(lds_u16(base - uint32_t(i) * kStageCPitch));
         }
+        mbar_arrive(bar(kBarGather));
+        ++band_idx;
       } else if (kind == kSatHi) {
         row_const = rc_hi;
       } else if (kind == kSatLo) {
@@ -480,9 +480,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 #pragma unroll
         for (int i = 0; i < 64; ++i) s[i] = i < valid ? s[i] : -INFINITY;
       }
-      float mx = s[0];
+      float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 4; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the two threads of a row agree on the row maximum
       const uint32_t xch = smem + kSmemXchg + uint32_t(j & 1) * 1024u;
       sts_f32(xch + uint32_t(g) * 512u + uint32_t(r) * 4u, mx);
@@ -493,8 +494,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       if (j == 0) {
         m_used = t_max;
       } else {
-        // The previous P.V has finished writing O.  Observed on every tile (it is long done by now) so that this thread
-        // never falls two phases behind the barrier, which a parity wait could not tell apart.
+        // The previous P.V has finished: O may be rescaled and the P columns overwritten.  Observed on every tile (it is
+        // long done by now) so that this thread never falls two phases behind the barrier, which a parity wait could
+        // not tell apart.
         wait(bar(kBarO), uint32_t(j - 1) & 1u);
         tc_fence_after();
         const bool need = t_max > m_used + 8.f;
@@ -515,23 +517,23 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         }
       }
       const float off = row_const * args.scale_log2 - m_used;
-      float l_add = 0.f;
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
         s[i] = ex2(fmaf(s[i], args.scale_log2, off));
-        l_add += s[i];
+        l4[i & 3] += s[i];
       }
-      l_run += l_add;
-      // P as bf16 pairs over this group's own S columns (first 32 of its 64)
+      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      // P as bf16 pairs: this group's 64 keys -> 32 columns of the P area
       if (ok) {
         uint32_t p[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) p[i] = pack_bf16x2(s[2 * i], s[2 * i + 1]);
-        tmem_st32(tmem_lane + sbuf_col(buf) + 64 * g, p);
+        tmem_st32(tmem_lane + kColP + 32 * g, p);
         tmem_wait_st();
       }
       tc_fence_before();
-      mbar_arrive(bar(kBarP + buf));
+      mbar_arrive(bar(kBarP));
     }
 
     // ---- epilogue: combine the two row sums, O / l, write this group's 32 output columns ----
