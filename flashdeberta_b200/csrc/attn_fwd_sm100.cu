@@ -8,8 +8,9 @@
 // producer and drain groups to the softmax groups with setmaxnreg):
 //   warps 0-3   softmax group 0: thread r owns row r of the tile, keys   0..63  of every 128-key tile
 //   warps 4-7   softmax group 1: thread r owns row r of the tile, keys  64..127
-//   warp  8     lane 0 issues every tcgen05.mma (and the warp allocates tensor memory)
+//   warp  8     lane 0 issues the score-side tcgen05.mma: S = Q.K^T and the position products (the warp allocates TMEM)
 //   warp  9     lane 0 issues every TMA load: Q once, K/V double-buffered, position-table windows
+//   warp  10    lane 0 issues O += P.V
 //   warps 12-15 drain group: moves the c2p product of a band tile from tensor memory to shared memory (bf16)
 // Tensor memory (512 columns): O 64 | P 64 | S 128 | R 256 (position products of a band tile).
 //
@@ -53,7 +54,7 @@ using namespace ptx;
 constexpr int kSoftmaxThreads = 256;
 constexpr int kDrainThreads = 128;
 constexpr int kThreads = 512;            // four warpgroups: softmax 0, softmax 1, producers (warps 10, 11 idle), drain
-constexpr int kMmaWarp = 8, kTmaWarp = 9, kDrainWarp0 = 12;
+constexpr int kMmaWarp = 8, kTmaWarp = 9, kPvWarp = 10, kDrainWarp0 = 12;
 // 128 registers per thread at launch; after setmaxnreg: 40 * 128 + 72 * 128 + 200 * 256 = 65536
 constexpr int kProducerRegs = 40, kDrainRegs = 72, kSoftmaxRegs = 200;
 constexpr uint32_t kTmemCols = 512;
@@ -110,7 +111,18 @@ struct alignas(64) FwdArgs {
   int batch, heads, packed, max_seqlen;
   int sat_lo, sat_hi, d_first, xrows;
   float scale_log2;  // sm_scale * log2(e)
+#ifdef FDB_TRACE
+  long long* trace;  // [role 0..3][tile 0..63][event 0..7] clock64 stamps of CTA (0, 0)
+#endif
 };
+
+#ifdef FDB_TRACE
+#define FDB_STAMP(role, tile, ev) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && args.trace != nullptr && (tile) < 64) \
+         args.trace[((role) * 64 + (tile)) * 8 + (ev)] = clock64(); } while (0)
+#else
+#define FDB_STAMP(role, tile, ev) do {} while (0)
+#endif
 
 enum TileKind : int { kPlain = 0, kSatHi = 1, kSatLo = 2, kBand = 3 };
 
@@ -286,8 +298,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         for (int j = 0; j < num_kt; ++j) {
           const int s = j & 1;
           const uint32_t use = uint32_t(j >> 1);  // how often this stage was used before
+          FDB_STAMP(3, j, 0);
           if (j >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
           if (!ok) break;
+          FDB_STAMP(3, j, 1);
           mbar_expect_tx(bar(kBarK + s), 16384);
           tma_load_3d(smem + kSmemK + s * 16384, &args.tm_k, bar(kBarK + s), 0, head, seq_row0 + j * kTileN);
           if (tile_kind(j) == kBand) {
@@ -301,39 +315,48 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           }
           if (j >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
           if (!ok) break;
+          FDB_STAMP(3, j, 2);
           mbar_expect_tx(bar(kBarV + s), 16384);
           tma_load_3d(smem + kSmemV + s * 16384, &args.tm_v, bar(kBarV + s), 0, head, seq_row0 + j * kTileN);
         }
       }
       __syncwarp();  // lanes 1-31 wait here for lane 0: the block-wide barrier below must be reached by whole warps
     } else if (warp == kMmaWarp) {
-      // ================================================= MMA issuer =====================================================
+      // ================================================= score MMA issuer ===============================================
+      // S = Q.K^T (+ saturated p2c) and the position products of band tiles.  Descriptors are built once; per MMA only the
+      // start-address field moves (a 64-bit add), which keeps the single issuing thread short of instructions.
       if (lane == 0) {
         auto wait = [&](uint32_t b, uint32_t parity) {
           if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
         };
         const uint32_t idesc_s = instr_desc(128, 128, 1, 0, 0);
         const uint32_t idesc_p2c = instr_desc(128, 32, 1, 0, 0);
-        const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
+        const uint64_t dq = smem_desc_sw128(smem + kSmemQ, 1024, 16);
+        const uint64_t dk0 = smem_desc_sw128(smem + kSmemK, 1024, 16);
+        const uint64_t dwk = smem_desc_sw128(smem + kSmemWinK, 1024, 16);
+        const uint64_t dwq = smem_desc_sw128(smem + kSmemWinQ, 1024, 16);
+        const uint64_t dsat = smem_desc_sw128(smem + kSmemSat, 0, 16);  // group stride 0: every 8-row group is the same rows
         int band_idx = 0;
-        // Scores (and position products) of tile j.  The caller has made sure S and R are free.
-        auto issue_scores = [&](int j) {
+        wait(bar(kBarQ), 0);
+#pragma unroll 1
+        for (int j = 0; j < num_kt; ++j) {
           const int kind = tile_kind(j);
           const int s = j & 1;
-          const uint32_t kq = smem + kSmemQ, kk = smem + kSmemK + s * 16384;
+          const uint64_t dk = dk0 + uint64_t(s) * (16384u >> 4);
+          // both softmax groups hold tile j-1 in registers: S and R are free
+          if (j > 0) wait(bar(kBarSFree), uint32_t(j - 1) & 1u);
           wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
           if (kind == kBand) {
             wait(bar(kBarWin), uint32_t(band_idx) & 1u);
             tc_fence_after();
             if (ok && has_c2p) {
               // c2pT[p][m] = X_k[p].Q[m]: two 128-position blocks -> R columns [0,128) and [128,256)
-#pragma unroll 1
+#pragma unroll
               for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)
-                  mma_bf16(tmem_base + kColR + blk * 128,
-                           smem_desc_sw128(smem + kSmemWinK + blk * 16384 + ks * 32, 1024, 16),
-                           smem_desc_sw128(kq + ks * 32, 1024, 16), idesc_s, ks > 0);
+                  mma_bf16(tmem_base + kColR + blk * 128, dwk + uint64_t((blk * 16384 + ks * 32) >> 4),
+                           dq + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             }
             mma_commit(bar(kBarC2p));
             wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
@@ -341,14 +364,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             if (ok && has_p2c) {
               // product (b, t) = X_q[32(3-b+t) .. +128) . K[32b .. +32)^T  -> 32 columns at R + 32(2b+t)
 #pragma unroll 1
-              for (int b = 0; b < 4; ++b)
-#pragma unroll 1
-                for (int t = 0; t < 2; ++t)
+              for (int b = 0; b < 4; ++b) {
+                const uint64_t dkb = dk + uint64_t(b) * (4096u >> 4);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                  const uint64_t dwb = dwq + uint64_t(3 - b + t) * (4096u >> 4);
 #pragma unroll
                   for (int ks = 0; ks < 4; ++ks)
-                    mma_bf16(tmem_base + kColR + 32 * (2 * b + t),
-                             smem_desc_sw128(smem + kSmemWinQ + 4096 * (3 - b + t) + ks * 32, 1024, 16),
-                             smem_desc_sw128(kk + 4096 * b + ks * 32, 1024, 16), idesc_p2c, ks > 0);
+                    mma_bf16(tmem_base + kColR + 32 * (2 * b + t), dwb + uint64_t((ks * 32) >> 4),
+                             dkb + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
+                }
+              }
             }
             ++band_idx;
           } else {
@@ -357,42 +383,45 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           if (ok) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmem_base + kColS, smem_desc_sw128(kq + ks * 32, 1024, 16),
-                       smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, ks > 0);
+              mma_bf16(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             if (has_p2c && (kind == kSatHi || kind == kSatLo)) {
-              const uint32_t sat = smem + kSmemSat + (kind == kSatHi ? 0u : 1024u);
+              const uint64_t ds = dsat + uint64_t(kind == kSatHi ? 0u : (1024u >> 4));
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks)  // every 8-row group of the operand is the same 8 rows: group stride 0
-                mma_bf16(tmem_base + kColS, smem_desc_sw128(sat + ks * 32, 0, 16),
-                         smem_desc_sw128(kk + ks * 32, 1024, 16), idesc_s, 1);
+              for (int ks = 0; ks < 4; ++ks)
+                mma_bf16(tmem_base + kColS, ds + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, 1);
             }
           }
           mma_commit(bar(kBarS));
           mma_commit(bar(kBarKFree + s));
           if (kind == kBand) mma_commit(bar(kBarWinFree));
+          FDB_STAMP(2, j, 0);
+        }
+      }
+      __syncwarp();  // as above
+    } else if (warp == kPvWarp) {
+      // ================================================= P.V MMA issuer =================================================
+      if (lane == 0) {
+        auto wait = [&](uint32_t b, uint32_t parity) {
+          if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
         };
-
-        wait(bar(kBarQ), 0);
-        issue_scores(0);
+        const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
+        const uint64_t dv0 = smem_desc_sw128(smem + kSmemV, 1024, 1024);
+#pragma unroll 1
         for (int j = 0; j < num_kt; ++j) {
-          if (j + 1 < num_kt) {
-            // as soon as both softmax groups hold tile j in registers, S and R are free: scores of tile j+1
-            wait(bar(kBarSFree), uint32_t(j) & 1u);
-            issue_scores(j + 1);
-          }
-          // O += P.V once both groups have written P
-          wait(bar(kBarP), uint32_t(j) & 1u);
+          const uint64_t dv = dv0 + uint64_t(j & 1) * (16384u >> 4);
           wait(bar(kBarV + (j & 1)), uint32_t(j >> 1) & 1u);
+          wait(bar(kBarP), uint32_t(j) & 1u);  // both groups have written P
           tc_fence_after();
+          FDB_STAMP(2, j, 3);
           if (ok) {
-            const uint32_t vv = smem + kSmemV + (j & 1) * 16384;
-#pragma unroll 2
+#pragma unroll
             for (int ks = 0; ks < 8; ++ks)
-              mma_bf16_ts(tmem_base + kColO, tmem_base + kColP + 8 * ks,
-                          smem_desc_sw128(vv + ks * 2048, 1024, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+              mma_bf16_ts(tmem_base + kColO, tmem_base + kColP + 8 * ks, dv + uint64_t((ks * 2048) >> 4), idesc_pv,
+                          (j > 0 || ks > 0) ? 1u : 0u);
           }
           mma_commit(bar(kBarO));
           mma_commit(bar(kBarVFree + (j & 1)));
+          FDB_STAMP(2, j, 5);
         }
       }
       __syncwarp();  // as above
@@ -428,8 +457,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       const int n0 = j * kTileN;
       const int kind = tile_kind(j);
 
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 0);
       wait(bar(kBarS), uint32_t(j) & 1u);
       tc_fence_after();
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 1);
 
       // ---- this thread's 64 scores (+ p2c through the quadrant shuffle) into registers, then S and R are released ----
       float s[64];
@@ -458,6 +489,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       }
       tc_fence_before();
       mbar_arrive(bar(kBarSFree));
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 2);
 
       float row_const = 0.f;
       if (kind == kBand) {
@@ -487,7 +519,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       // the two threads of a row agree on the row maximum
       const uint32_t xch = smem + kSmemXchg + uint32_t(j & 1) * 1024u;
       sts_f32(xch + uint32_t(g) * 512u + uint32_t(r) * 4u, mx);
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 3);
       bar_sync(1, kSoftmaxThreads);
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 4);
       mx = fmaxf(mx, lds_f32(xch + uint32_t(g ^ 1) * 512u + uint32_t(r) * 4u));
 
       const float t_max = (mx + row_const) * args.scale_log2;
@@ -516,6 +550,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           }
         }
       }
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 5);
       const float off = row_const * args.scale_log2 - m_used;
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -524,6 +559,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         l4[i & 3] += s[i];
       }
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 6);
       // P as bf16 pairs: this group's 64 keys -> 32 columns of the P area
       if (ok) {
         uint32_t p[32];
@@ -534,6 +570,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       }
       tc_fence_before();
       mbar_arrive(bar(kBarP));
+      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 7);
     }
 
     // ---- epilogue: combine the two row sums, O / l, write this group's 32 output columns ----
@@ -606,6 +643,12 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   a.batch = p.batch; a.heads = p.heads; a.packed = p.cu_seqlens != nullptr; a.max_seqlen = p.max_seqlen;
   a.sat_lo = g.sat_lo; a.sat_hi = g.sat_hi; a.d_first = g.d_first; a.xrows = g.rows;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
+#ifdef FDB_TRACE
+  {
+    const char* tp = std::getenv("FDB_TRACE_PTR");
+    a.trace = tp ? reinterpret_cast<long long*>(std::strtoull(tp, nullptr, 0)) : nullptr;
+  }
+#endif
 
   const int64_t dense_tiles = (int64_t)p.batch * ((p.max_seqlen + kTileM - 1) / kTileM);
   int64_t slots = dense_tiles;
