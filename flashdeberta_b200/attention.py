@@ -45,6 +45,9 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         self._pos_cache = None
+        config = args[0] if args else kwargs.get("config")
+        # FP8-e4m3 attention (per-head amax scales); a new switch, the reference has no FP8 path
+        self.attn_fp8 = bool(getattr(config, "attn_fp8", False))
 
     # -- position tables ------------------------------------------------------------------------------------------------
     def _heads_first(self, x: torch.Tensor) -> torch.Tensor:
@@ -106,7 +109,12 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         if in_dtype != torch.bfloat16:
             q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
         seq_lens = lengths_from_mask(attention_mask)
-        out = ops.attn_fwd_op(q, k, v, pos_key, pos_query, None, seq_lens, L, sm_scale, buckets, max_rel)
+        if self.attn_fp8:
+            out = ops.disentangled_attention_fp8(q, k, v, pos_key, pos_query, seq_lens=seq_lens, max_seqlen=L,
+                                                 sm_scale=sm_scale, position_buckets=buckets,
+                                                 max_relative_positions=max_rel)
+        else:
+            out = ops.attn_fwd_op(q, k, v, pos_key, pos_query, None, seq_lens, L, sm_scale, buckets, max_rel)
         out = out.view(B, L, H * D)
         if in_dtype != torch.bfloat16:
             out = out.to(in_dtype)

@@ -509,18 +509,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_serial_kernel(const __gr
 }  // namespace
 
 int launch_attn_fwd_serial(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream) {
-  if (p.dtype != FDB_BF16) return fail(FDB_ERR_UNSUPPORTED, "fused kernel: dtype %d is not built yet", p.dtype);
+  if (p.dtype != FDB_BF16) return fail(FDB_ERR_UNSUPPORTED, "the serial kernel takes bf16 inputs only");
   FwdArgs a;
   char* ws = static_cast<char*>(p.workspace);
   int rc;
-  if ((rc = make_map_rows(&a.tm_q, p.q, p.total_rows, p.heads, p.q_row_stride, p.q_head_stride, kTileM, "q"))) return rc;
-  if ((rc = make_map_rows(&a.tm_k, p.k, p.total_rows, p.heads, p.k_row_stride, p.k_head_stride, kTileN, "k"))) return rc;
-  if ((rc = make_map_rows(&a.tm_v, p.v, p.total_rows, p.heads, p.v_row_stride, p.v_head_stride, kTileN, "v"))) return rc;
+  if ((rc = make_map_rows(&a.tm_q, p.q, p.total_rows, p.heads, p.q_row_stride, p.q_head_stride, kTileM, false, "q"))) return rc;
+  if ((rc = make_map_rows(&a.tm_k, p.k, p.total_rows, p.heads, p.k_row_stride, p.k_head_stride, kTileN, false, "k"))) return rc;
+  if ((rc = make_map_rows(&a.tm_v, p.v, p.total_rows, p.heads, p.v_row_stride, p.v_head_stride, kTileN, false, "v"))) return rc;
   a.xk = p.pos_key ? reinterpret_cast<const __nv_bfloat16*>(ws + w.exp_key) : nullptr;
   a.xq = p.pos_query ? reinterpret_cast<const __nv_bfloat16*>(ws + w.exp_query) : nullptr;
   // a map is always encoded so the kernel argument is well formed; an unused one points at q
-  if (a.xk) { if ((rc = make_map_table(&a.tm_xk, a.xk, g.rows, p.heads, "expanded pos_key"))) return rc; } else a.tm_xk = a.tm_q;
-  if (a.xq) { if ((rc = make_map_table(&a.tm_xq, a.xq, g.rows, p.heads, "expanded pos_query"))) return rc; } else a.tm_xq = a.tm_q;
+  if (a.xk) { if ((rc = make_map_table(&a.tm_xk, a.xk, g.rows, p.heads, false, "expanded pos_key"))) return rc; } else a.tm_xk = a.tm_q;
+  if (a.xq) { if ((rc = make_map_table(&a.tm_xq, a.xq, g.rows, p.heads, false, "expanded pos_query"))) return rc; } else a.tm_xq = a.tm_q;
   a.out = static_cast<__nv_bfloat16*>(p.out);
   a.o_rs = p.out_row_stride; a.o_hs = p.out_head_stride;
   a.seq_info = reinterpret_cast<const int32_t*>(ws + w.seq_info);

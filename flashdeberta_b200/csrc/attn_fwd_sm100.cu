@@ -104,8 +104,10 @@ struct alignas(64) FwdArgs {
   int64_t o_rs, o_hs;
   const int32_t* seq_info;    // [batch][2] first row, length
   const int32_t* tile_first;  // [batch+1]
-  const __nv_bfloat16* xk;    // expanded pos_key   (heads, xrows, 64)
-  const __nv_bfloat16* xq;    // expanded pos_query
+  const void* xk;             // expanded pos_key   (heads, xrows, 64) bf16 or e4m3
+  const void* xq;             // expanded pos_query
+  const float *q_scale, *k_scale, *v_scale;  // e4m3 only: [seq * heads + head]
+  const float *xk_scale, *xq_scale;          // e4m3 only: [head]
   float* lse;
   int32_t* status;
   int batch, heads, packed, max_seqlen;
@@ -125,6 +127,29 @@ struct alignas(64) FwdArgs {
 #endif
 
 enum TileKind : int { kPlain = 0, kSatHi = 1, kSatLo = 2, kBand = 3 };
+
+// What changes between the bf16 and the e4m3 build of the kernel: bytes per 64-element row (128 / 64, hence 128-byte or
+// 64-byte swizzle and 1024- or 512-byte 8-row groups), elements per MMA along K (16 / 32) and the MMA kind.
+template <bool F8> struct Geo {
+  static constexpr uint32_t kRow = F8 ? 64u : 128u;          // bytes per row of 64 elements
+  static constexpr uint32_t kTile = 128u * kRow;             // a 128-row tile
+  static constexpr uint32_t kWin = 256u * kRow;              // a 256-row window
+  static constexpr uint32_t kGroup = 8u * kRow;              // 8-row group (stride byte offset)
+  static constexpr int kSteps = F8 ? 2 : 4;                  // MMAs along head_dim 64
+  static constexpr int kPvSteps = F8 ? 4 : 8;                // MMAs along 128 keys
+  static constexpr uint32_t kPColsPerStep = 8u;              // TMEM columns of P one P.V MMA reads (16 bf16 / 32 e4m3)
+  static constexpr uint32_t kPCols = F8 ? 16u : 32u;         // TMEM columns of P per softmax group (64 keys)
+  static constexpr int kFmt = F8 ? 0 : 1;                    // instruction-descriptor operand format: e4m3 / bf16
+  __device__ static __forceinline__ uint64_t desc(uint32_t addr, uint32_t group_stride) {
+    return F8 ? smem_desc_sw64(addr, group_stride, 16) : smem_desc_sw128(addr, group_stride, 16);
+  }
+  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    if constexpr (F8) mma_f8(d, a, b, idesc, acc); else mma_bf16(d, a, b, idesc, acc);
+  }
+  __device__ static __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    if constexpr (F8) mma_f8_ts(d, a, b, idesc, acc); else mma_bf16_ts(d, a, b, idesc, acc);
+  }
+};
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
@@ -167,7 +192,30 @@ __device__ __forceinline__ float dot_q_row(uint32_t q_row_addr, int row, const _
   return acc;
 }
 
+// the same for e4m3 rows (64 bytes, 64-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3))
+__device__ __forceinline__ float dot_q_row_f8(uint32_t q_row_addr, int row, const uint8_t* __restrict__ g) {
+  float acc = 0.f;
+  const uint4* g4 = reinterpret_cast<const uint4*>(g);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint4 a = lds_v4(q_row_addr + (uint32_t(c ^ ((row >> 1) & 3)) << 4));
+    const uint4 b = __ldg(g4 + c);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float fa[4], fb[4];
+      unpack_e4m3x4(aw[i], fa);
+      unpack_e4m3x4(bw[i], fb);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc = fmaf(fa[k], fb[k], acc);
+    }
+  }
+  return acc;
+}
+
+template <bool F8>
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_constant__ FwdArgs args) {
+  using G = Geo<F8>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem - smem_u32(smem_raw));
@@ -224,12 +272,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     fence_barrier_init();
   }
   if (has_p2c && tid < 128) {
-    // saturated pos_query rows, 8 identical 128-byte rows each, in the swizzled operand layout: tile 0 = last row, 1 = first
+    // saturated pos_query rows, 8 identical rows each, in the swizzled operand layout: tile 0 = last row, 1 = first
     const int t = tid >> 6, row = (tid >> 3) & 7, c = tid & 7;
-    const __nv_bfloat16* src = args.xq + ((int64_t)head * args.xrows + (t == 0 ? args.xrows - 1 : 0)) * kHeadDim;
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + c);
-    sts_v4(smem + kSmemSat + t * 1024 + row * 128 + (uint32_t(c ^ row) << 4), v.x, v.y, v.z, v.w);
+    const uint8_t* src = static_cast<const uint8_t*>(args.xq) +
+                         ((int64_t)head * args.xrows + (t == 0 ? args.xrows - 1 : 0)) * G::kRow;
+    if (c < int(G::kRow / 16)) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + c);
+      const uint32_t sw = F8 ? uint32_t(c ^ ((row >> 1) & 3)) : uint32_t(c ^ row);
+      sts_v4(smem + kSmemSat + t * 1024 + row * G::kRow + (sw << 4), v.x, v.y, v.z, v.w);
+    }
     fence_proxy_async_smem();
+  }
+  // e4m3: value = stored * scale.  The three score terms carry different scale products; they are brought to the one of
+  // Q.K^T (ratio_c, ratio_p) when they are added, and that product goes into the softmax scale.
+  float c_eff = args.scale_log2, ratio_c = 1.f, ratio_p = 1.f, v_scale = 1.f;
+  if constexpr (F8) {
+    const float sq = __ldg(args.q_scale + (int64_t)seq * args.heads + head);
+    const float sk = __ldg(args.k_scale + (int64_t)seq * args.heads + head);
+    v_scale = __ldg(args.v_scale + (int64_t)seq * args.heads + head);
+    c_eff = args.scale_log2 * sq * sk;
+    if (has_c2p) ratio_c = __ldg(args.xk_scale + head) / sk;
+    if (has_p2c) ratio_p = __ldg(args.xq_scale + head) / sq;
   }
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -292,7 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
         };
         tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
-        mbar_expect_tx(bar(kBarQ), 16384);
+        mbar_expect_tx(bar(kBarQ), G::kTile);
         tma_load_3d(smem + kSmemQ, &args.tm_q, bar(kBarQ), 0, head, seq_row0 + m0);
         int band_idx = 0;
         for (int j = 0; j < num_kt; ++j) {
@@ -302,13 +365,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           if (j >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
           if (!ok) break;
           FDB_STAMP(3, j, 1);
-          mbar_expect_tx(bar(kBarK + s), 16384);
+          mbar_expect_tx(bar(kBarK + s), G::kTile);
           tma_load_3d(smem + kSmemK + s * 16384, &args.tm_k, bar(kBarK + s), 0, head, seq_row0 + j * kTileN);
           if (tile_kind(j) == kBand) {
             if (band_idx > 0) wait(bar(kBarWinFree), uint32_t(band_idx - 1) & 1u);
             if (!ok) break;
             const int u0 = m0 - j * kTileN - (kTileN - 1) - args.d_first;
-            mbar_expect_tx(bar(kBarWin), (has_c2p ? 32768u : 0u) + (has_p2c ? 32768u : 0u));
+            mbar_expect_tx(bar(kBarWin), (has_c2p ? G::kWin : 0u) + (has_p2c ? G::kWin : 0u));
             if (has_c2p) tma_load_3d(smem + kSmemWinK, &args.tm_xk, bar(kBarWin), 0, u0, head);
             if (has_p2c) tma_load_3d(smem + kSmemWinQ, &args.tm_xq, bar(kBarWin), 0, u0, head);
             ++band_idx;
@@ -316,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           if (j >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
           if (!ok) break;
           FDB_STAMP(3, j, 2);
-          mbar_expect_tx(bar(kBarV + s), 16384);
+          mbar_expect_tx(bar(kBarV + s), G::kTile);
           tma_load_3d(smem + kSmemV + s * 16384, &args.tm_v, bar(kBarV + s), 0, head, seq_row0 + j * kTileN);
         }
       }
@@ -329,20 +392,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         auto wait = [&](uint32_t b, uint32_t parity) {
           if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
         };
-        const uint32_t idesc_s = instr_desc(128, 128, 1, 0, 0);
-        const uint32_t idesc_p2c = instr_desc(128, 32, 1, 0, 0);
-        const uint64_t dq = smem_desc_sw128(smem + kSmemQ, 1024, 16);
-        const uint64_t dk0 = smem_desc_sw128(smem + kSmemK, 1024, 16);
-        const uint64_t dwk = smem_desc_sw128(smem + kSmemWinK, 1024, 16);
-        const uint64_t dwq = smem_desc_sw128(smem + kSmemWinQ, 1024, 16);
-        const uint64_t dsat = smem_desc_sw128(smem + kSmemSat, 0, 16);  // group stride 0: every 8-row group is the same rows
+        const uint32_t idesc_s = instr_desc(128, 128, G::kFmt, 0, 0);
+        const uint32_t idesc_p2c = instr_desc(128, 32, G::kFmt, 0, 0);
+        const uint64_t dq = G::desc(smem + kSmemQ, G::kGroup);
+        const uint64_t dk0 = G::desc(smem + kSmemK, G::kGroup);
+        const uint64_t dwk = G::desc(smem + kSmemWinK, G::kGroup);
+        const uint64_t dwq = G::desc(smem + kSmemWinQ, G::kGroup);
+        const uint64_t dsat = G::desc(smem + kSmemSat, 0);  // group stride 0: every 8-row group is the same rows
         int band_idx = 0;
         wait(bar(kBarQ), 0);
 #pragma unroll 1
         for (int j = 0; j < num_kt; ++j) {
           const int kind = tile_kind(j);
           const int s = j & 1;
-          const uint64_t dk = dk0 + uint64_t(s) * (16384u >> 4);
+          const uint64_t dk = dk0 + uint64_t(s) * (16384u >> 4);  // stages are 16 KB apart in either build
           // both softmax groups hold tile j-1 in registers: S and R are free
           if (j > 0) wait(bar(kBarSFree), uint32_t(j - 1) & 1u);
           wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
@@ -354,9 +417,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 #pragma unroll
               for (int blk = 0; blk < 2; ++blk)
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                  mma_bf16(tmem_base + kColR + blk * 128, dwk + uint64_t((blk * 16384 + ks * 32) >> 4),
-                           dq + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
+                for (int ks = 0; ks < G::kSteps; ++ks)
+                  G::mma(tmem_base + kColR + blk * 128, dwk + uint64_t((blk * G::kTile + ks * 32) >> 4),
+                         dq + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             }
             mma_commit(bar(kBarC2p));
             wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
@@ -365,14 +428,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
               // product (b, t) = X_q[32(3-b+t) .. +128) . K[32b .. +32)^T  -> 32 columns at R + 32(2b+t)
 #pragma unroll 1
               for (int b = 0; b < 4; ++b) {
-                const uint64_t dkb = dk + uint64_t(b) * (4096u >> 4);
+                const uint64_t dkb = dk + uint64_t(b) * ((32u * G::kRow) >> 4);
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
-                  const uint64_t dwb = dwq + uint64_t(3 - b + t) * (4096u >> 4);
+                  const uint64_t dwb = dwq + uint64_t(3 - b + t) * ((32u * G::kRow) >> 4);
 #pragma unroll
-                  for (int ks = 0; ks < 4; ++ks)
-                    mma_bf16(tmem_base + kColR + 32 * (2 * b + t), dwb + uint64_t((ks * 32) >> 4),
-                             dkb + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
+                  for (int ks = 0; ks < G::kSteps; ++ks)
+                    G::mma(tmem_base + kColR + 32 * (2 * b + t), dwb + uint64_t((ks * 32) >> 4),
+                           dkb + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
                 }
               }
             }
@@ -382,13 +445,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           }
           if (ok) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              mma_bf16(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
+            for (int ks = 0; ks < G::kSteps; ++ks)
+              G::mma(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             if (has_p2c && (kind == kSatHi || kind == kSatLo)) {
+              // bf16: accumulated straight into S.  e4m3: the term has its own scale, so it goes to the (idle) product
+              // area and the softmax threads add it with the ratio of the scales.
               const uint64_t ds = dsat + uint64_t(kind == kSatHi ? 0u : (1024u >> 4));
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                mma_bf16(tmem_base + kColS, ds + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, 1);
+              for (int ks = 0; ks < G::kSteps; ++ks)
+                G::mma(tmem_base + (F8 ? kColR : kColS), ds + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4),
+                       idesc_s, (F8 ? ks > 0 : 1));
             }
           }
           mma_commit(bar(kBarS));
@@ -404,8 +470,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         auto wait = [&](uint32_t b, uint32_t parity) {
           if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
         };
-        const uint32_t idesc_pv = instr_desc(128, 64, 1, 0, 1);
-        const uint64_t dv0 = smem_desc_sw128(smem + kSmemV, 1024, 1024);
+        const uint32_t idesc_pv = instr_desc(128, 64, G::kFmt, 0, 1);
+        const uint64_t dv0 = G::desc(smem + kSmemV, G::kGroup);  // V is the MN-major operand: keys run along K
 #pragma unroll 1
         for (int j = 0; j < num_kt; ++j) {
           const uint64_t dv = dv0 + uint64_t(j & 1) * (16384u >> 4);
@@ -415,9 +481,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           FDB_STAMP(2, j, 3);
           if (ok) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              mma_bf16_ts(tmem_base + kColO, tmem_base + kColP + 8 * ks, dv + uint64_t((ks * 2048) >> 4), idesc_pv,
-                          (j > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < G::kPvSteps; ++ks)  // one step = 2048 bytes of V in either build (16 x 128 B, 32 x 64 B)
+              G::mma_ts(tmem_base + kColO, tmem_base + kColP + G::kPColsPerStep * ks, dv + uint64_t((ks * 2048) >> 4),
+                        idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           }
           mma_commit(bar(kBarO));
           mma_commit(bar(kBarVFree + (j & 1)));
@@ -444,10 +510,16 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     wait(bar(kBarQ), 0);
     float rc_lo = 0.f, rc_hi = 0.f;  // saturated c2p terms of this row: Q[m].X_k[first row], Q[m].X_k[last row]
     if (has_c2p && ok) {
-      const __nv_bfloat16* xk_h = args.xk + (int64_t)head * args.xrows * kHeadDim;
-      const uint32_t q_row = smem + kSmemQ + uint32_t(r) * 128u;
-      rc_lo = dot_q_row(q_row, r, xk_h);
-      rc_hi = dot_q_row(q_row, r, xk_h + (int64_t)(args.xrows - 1) * kHeadDim);
+      const uint32_t q_row = smem + kSmemQ + uint32_t(r) * G::kRow;
+      if constexpr (F8) {
+        const uint8_t* xk_h = static_cast<const uint8_t*>(args.xk) + (int64_t)head * args.xrows * kHeadDim;
+        rc_lo = ratio_c * dot_q_row_f8(q_row, r, xk_h);
+        rc_hi = ratio_c * dot_q_row_f8(q_row, r, xk_h + (int64_t)(args.xrows - 1) * kHeadDim);
+      } else {
+        const __nv_bfloat16* xk_h = static_cast<const __nv_bfloat16*>(args.xk) + (int64_t)head * args.xrows * kHeadDim;
+        rc_lo = dot_q_row(q_row, r, xk_h);
+        rc_hi = dot_q_row(q_row, r, xk_h + (int64_t)(args.xrows - 1) * kHeadDim);
+      }
     }
 
     uint32_t band_idx = 0;
@@ -479,8 +551,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           for (int c = 0; c < 32; ++c) {
             const uint32_t x = (lane + c <= 30) ? t1[c] : t0[c];
             const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - c) & 31);
-            s[32 * ch + c] = __uint_as_float(a[c]) + __uint_as_float(y);
+            s[32 * ch + c] = fmaf(__uint_as_float(y), ratio_p, __uint_as_float(a[c]));
           }
+        } else if (F8 && has_p2c && (kind == kSatHi || kind == kSatLo)) {
+          // e4m3: the saturated p2c term of these keys sits in the product area (same value in every row)
+          uint32_t t0[32];
+          if (ok) {
+            tmem_ld32(tmem_lane + kColR + 64 * g + 32 * ch, t0);
+            tmem_wait_ld();
+          }
+#pragma unroll
+          for (int c = 0; c < 32; ++c) s[32 * ch + c] = fmaf(__uint_as_float(t0[c]), ratio_p, __uint_as_float(a[c]));
         } else {
           if (ok) tmem_wait_ld();
 #pragma unroll
@@ -498,7 +579,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           // c2p[m][i] sits at stage[(m + 127 - i)][m]
           const uint32_t base = smem + kSmemStageC + uint32_t(r + 127 - 64 * g) * kStageCPitch + uint32_t(r) * 2u;
 #pragma unroll
-          for (int i = 0; i < 64; ++i) s[i] += bf16_bits_to_f32(lds_u16(base - uint32_t(i) * kStageCPitch));
+          for (int i = 0; i < 64; ++i) s[i] = fmaf(bf16_bits_to_f32(lds_u16(base - uint32_t(i) * kStageCPitch)), ratio_c, s[i]);
         }
         mbar_arrive(bar(kBarGather));
         ++band_idx;
@@ -524,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 4);
       mx = fmaxf(mx, lds_f32(xch + uint32_t(g ^ 1) * 512u + uint32_t(r) * 4u));
 
-      const float t_max = (mx + row_const) * args.scale_log2;
+      const float t_max = (mx + row_const) * c_eff;
       if (j == 0) {
         m_used = t_max;
       } else {
@@ -533,7 +614,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         // not tell apart.
         wait(bar(kBarO), uint32_t(j - 1) & 1u);
         tc_fence_after();
-        const bool need = t_max > m_used + 8.f;
+        // bf16: O is rescaled only when the maximum moved by more than 2^8 (P <= 256 is harmless in bf16).
+        // e4m3: P is stored as 2^8 * exp2(.), so it has to stay <= 1: rescale whenever the maximum moves.
+        const bool need = t_max > m_used + (F8 ? 0.f : 8.f);
         if (__any_sync(0xffffffffu, need)) {  // warp-uniform, and the same in both groups: rescale O of these 32 rows
           const float m_new = fmaxf(m_used, t_max);
           const float alpha = ex2(m_used - m_new);
@@ -551,21 +634,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         }
       }
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 5);
-      const float off = row_const * args.scale_log2 - m_used;
+      const float off = row_const * c_eff - m_used + (F8 ? 8.f : 0.f);
       float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        s[i] = ex2(fmaf(s[i], args.scale_log2, off));
+        s[i] = ex2(fmaf(s[i], c_eff, off));
         l4[i & 3] += s[i];
       }
       l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 6);
-      // P as bf16 pairs: this group's 64 keys -> 32 columns of the P area
+      // P for this group's 64 keys: 32 columns of bf16 pairs, or 16 columns of e4m3 quadruples
       if (ok) {
-        uint32_t p[32];
+        if constexpr (F8) {
+          uint32_t p[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) p[i] = pack_bf16x2(s[2 * i], s[2 * i + 1]);
-        tmem_st32(tmem_lane + kColP + 32 * g, p);
+          for (int i = 0; i < 16; ++i) p[i] = pack_e4m3x4(s[4 * i], s[4 * i + 1], s[4 * i + 2], s[4 * i + 3]);
+          tmem_st16(tmem_lane + kColP + 16 * g, p);
+        } else {
+          uint32_t p[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) p[i] = pack_bf16x2(s[2 * i], s[2 * i + 1]);
+          tmem_st32(tmem_lane + kColP + 32 * g, p);
+        }
         tmem_wait_st();
       }
       tc_fence_before();
@@ -582,7 +672,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     if (ok) {
       const bool valid = my_row < len;
       const bool pad = !valid && my_row < row_limit;  // dense padding rows inside a partly valid tile get zeros
-      const float inv = valid ? 1.f / l_tot : 0.f;
+      const float inv = valid ? v_scale / l_tot : 0.f;
       uint32_t o[32];
       tmem_ld32(tmem_lane + kColO + 32 * g, o);  // whole warps execute this, whatever their rows
       tmem_wait_ld();
@@ -601,7 +691,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         }
         if (g == 0 && args.lse != nullptr)
           args.lse[(int64_t)(seq_row0 + my_row) * args.heads + head] =
-              valid ? (m_used + log2f(l_tot)) * 0.6931471805599453f : 0.f;
+              valid ? (m_used + log2f(l_tot) - (F8 ? 8.f : 0.f)) * 0.6931471805599453f : 0.f;
       }
     }
   }
@@ -621,20 +711,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 }  // namespace
 
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream) {
+  const bool f8 = p.dtype == FDB_E4M3;
   const char* which = std::getenv("FDB_ATTN_KERNEL");
-  if (which != nullptr && std::strcmp(which, "serial") == 0) return launch_attn_fwd_serial(p, g, w, stream);
-  if (p.dtype != FDB_BF16) return fail(FDB_ERR_UNSUPPORTED, "fused kernel: dtype %d is not built yet", p.dtype);
+  if (!f8 && which != nullptr && std::strcmp(which, "serial") == 0) return launch_attn_fwd_serial(p, g, w, stream);
   FwdArgs a;
   char* ws = static_cast<char*>(p.workspace);
   int rc;
-  if ((rc = make_map_rows(&a.tm_q, p.q, p.total_rows, p.heads, p.q_row_stride, p.q_head_stride, kTileM, "q"))) return rc;
-  if ((rc = make_map_rows(&a.tm_k, p.k, p.total_rows, p.heads, p.k_row_stride, p.k_head_stride, kTileN, "k"))) return rc;
-  if ((rc = make_map_rows(&a.tm_v, p.v, p.total_rows, p.heads, p.v_row_stride, p.v_head_stride, kTileN, "v"))) return rc;
-  a.xk = p.pos_key ? reinterpret_cast<const __nv_bfloat16*>(ws + w.exp_key) : nullptr;
-  a.xq = p.pos_query ? reinterpret_cast<const __nv_bfloat16*>(ws + w.exp_query) : nullptr;
+  if ((rc = make_map_rows(&a.tm_q, p.q, p.total_rows, p.heads, p.q_row_stride, p.q_head_stride, kTileM, f8, "q"))) return rc;
+  if ((rc = make_map_rows(&a.tm_k, p.k, p.total_rows, p.heads, p.k_row_stride, p.k_head_stride, kTileN, f8, "k"))) return rc;
+  if ((rc = make_map_rows(&a.tm_v, p.v, p.total_rows, p.heads, p.v_row_stride, p.v_head_stride, kTileN, f8, "v"))) return rc;
+  a.xk = p.pos_key ? ws + w.exp_key : nullptr;
+  a.xq = p.pos_query ? ws + w.exp_query : nullptr;
+  a.q_scale = p.q_scale; a.k_scale = p.k_scale; a.v_scale = p.v_scale;
+  a.xk_scale = p.pos_key_scale; a.xq_scale = p.pos_query_scale;
   // a map is always encoded so the kernel argument is well formed; an unused one points at q
-  if (a.xk) { if ((rc = make_map_table(&a.tm_xk, a.xk, g.rows, p.heads, "expanded pos_key"))) return rc; } else a.tm_xk = a.tm_q;
-  if (a.xq) { if ((rc = make_map_table(&a.tm_xq, a.xq, g.rows, p.heads, "expanded pos_query"))) return rc; } else a.tm_xq = a.tm_q;
+  if (a.xk) { if ((rc = make_map_table(&a.tm_xk, a.xk, g.rows, p.heads, f8, "expanded pos_key"))) return rc; } else a.tm_xk = a.tm_q;
+  if (a.xq) { if ((rc = make_map_table(&a.tm_xq, a.xq, g.rows, p.heads, f8, "expanded pos_query"))) return rc; } else a.tm_xq = a.tm_q;
   a.out = static_cast<__nv_bfloat16*>(p.out);
   a.o_rs = p.out_row_stride; a.o_hs = p.out_head_stride;
   a.seq_info = reinterpret_cast<const int32_t*>(ws + w.seq_info);
@@ -656,9 +748,10 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   if (slots <= 0) return FDB_OK;
   if (slots > 2147483647LL || p.heads > 65535) return fail(FDB_ERR_LIMIT, "grid too large");
 
-  cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+  auto kernel = f8 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  attn_fwd_kernel<<<dim3((unsigned)slots, p.heads), kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(a);
+  kernel<<<dim3((unsigned)slots, p.heads), kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "attn_fwd launch: %s", cudaGetErrorString(e));
   return FDB_OK;

@@ -25,32 +25,37 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (rows, heads, 64) bf16 tensor with element strides -> 3-D map (d, head, row), box 64 x 1 x box_rows, 128-byte swizzle
+// (rows, heads, 64) tensor with element strides -> 3-D map (d, head, row), box 64 x 1 x box_rows.
+// bf16: 128-byte rows, 128-byte swizzle.  e4m3 (`f8`): 64-byte rows, 64-byte swizzle.
 inline int make_map_rows(CUtensorMap* m, const void* base, int64_t rows, int heads, int64_t row_stride,
-                         int64_t head_stride, int box_rows, const char* what) {
+                         int64_t head_stride, int box_rows, bool f8, const char* what) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t esz = f8 ? 1 : 2;
   const cuuint64_t dims[3] = {64, (cuuint64_t)heads, (cuuint64_t)rows};
-  const cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)row_stride * 2};
+  const cuuint64_t strides[2] = {(cuuint64_t)head_stride * esz, (cuuint64_t)row_stride * esz};
   const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  const CUresult r = fn(m, f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        f8 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
   return FDB_OK;
 }
 
-// expanded table (heads, xrows, 64) bf16 contiguous -> 3-D map (d, row, head), box 64 x 256 x 1
-inline int make_map_table(CUtensorMap* m, const void* base, int xrows, int heads, const char* what) {
+// expanded table (heads, xrows, 64) contiguous -> 3-D map (d, row, head), box 64 x 256 x 1
+inline int make_map_table(CUtensorMap* m, const void* base, int xrows, int heads, bool f8, const char* what) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t row = f8 ? 64 : 128;
   const cuuint64_t dims[3] = {64, (cuuint64_t)xrows, (cuuint64_t)heads};
-  const cuuint64_t strides[2] = {128, (cuuint64_t)xrows * 128};
+  const cuuint64_t strides[2] = {row, (cuuint64_t)xrows * row};
   const cuuint32_t box[3] = {64, (cuuint32_t)kWindow, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  const CUresult r = fn(m, f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        f8 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
   return FDB_OK;

@@ -18,7 +18,7 @@ import torch
 from . import _lib, bucket
 
 __all__ = [
-    "disentangled_attention", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3",
+    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3",
     "check_status", "launch_count",
 ]
 
@@ -194,6 +194,43 @@ def disentangled_attention(
         # `keep` and `ws` were allocated on this stream, so the caching allocator reuses them in stream order
         del keep, ws
     return (out, lse) if return_lse else out
+
+
+def disentangled_attention_fp8(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    pos_key: Optional[torch.Tensor], pos_query: Optional[torch.Tensor],
+    *, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
+    max_seqlen: int, sm_scale: Optional[float] = None, position_buckets: int = -1, max_relative_positions: int = -1,
+):
+    """FP8 attention: bf16 inputs are scaled to float8-e4m3 with one amax-derived scale per (sequence, head) for q, k, v
+    and per head for the position tables, the fused kernel runs its MMAs in e4m3 with fp32 accumulation (P is stored as
+    2^8 * exp2(.) in e4m3), and the scales are folded back into the softmax scale and the output.  No counterpart in the
+    reference.  Returns bf16."""
+    if q.dim() == 4:
+        B, L = q.shape[0], q.shape[1]
+        slabs = torch.arange(0, (B + 1) * L, L, dtype=torch.int32, device=q.device)
+    else:
+        if cu_seqlens is None:
+            raise ValueError("packed inputs need cu_seqlens")
+        slabs = cu_seqlens.to(torch.int32)
+    q8, sq = quantize_e4m3(q, slabs)
+    k8, sk = quantize_e4m3(k, slabs)
+    v8, sv = quantize_e4m3(v, slabs)
+    scales = {"q_scale": sq, "k_scale": sk, "v_scale": sv}
+    tabs = {}
+    for name, t in (("pos_key", pos_key), ("pos_query", pos_query)):
+        if t is None:
+            tabs[name] = None
+            continue
+        H, R, D = t.shape
+        rows = t.contiguous().view(H * R, 1, D)
+        y, sc = quantize_e4m3(rows, torch.arange(0, (H + 1) * R, R, dtype=torch.int32, device=t.device))
+        tabs[name] = y.view(H, R, D)
+        scales[name + "_scale"] = sc.view(H)
+    return disentangled_attention(q8, k8, v8, tabs["pos_key"], tabs["pos_query"], cu_seqlens=cu_seqlens,
+                                  seq_lens=seq_lens, max_seqlen=max_seqlen, sm_scale=sm_scale,
+                                  position_buckets=position_buckets, max_relative_positions=max_relative_positions,
+                                  scales=scales)
 
 
 def disentangled_attention_static(
