@@ -364,6 +364,75 @@ def _oracle_rows(q, k, v, pk, pq, m0, n, sm):
 
 
 # ---------------------------------------------------------------------------------------------------------------------
+# FP8-e4m3 attention (no reference code exists; fp32 eager is the reference, a fake-quantised oracle the expectation)
+# ---------------------------------------------------------------------------------------------------------------------
+# Stated bounds.  Against the same math on operands rounded through e4m3 with the same per-(sequence, head) scales, what
+# is left is the e4m3 rounding of P: max-abs <= 3e-2, mean-abs <= 4e-3 on unit-variance inputs.  Against fp32 the operand
+# rounding itself dominates, so the kernel is held to 1.5x the error of that fake-quantised oracle plus the P bound.
+FP8_P_MAX, FP8_P_MEAN = 3e-2, 4e-3
+
+
+@pytest.mark.parametrize("B,L,H,lens,c2p,p2c", [
+    (1, 128, 1, None, False, False), (1, 128, 2, None, True, True), (2, 1000, 2, None, False, False),
+    (1, 1500, 2, None, True, True), (3, 900, 2, [900, 515, 1], True, True), (1, 1500, 1, None, True, False),
+    (1, 1500, 1, None, False, True),
+])
+def test_fp8_fused_vs_fake_quantised_oracle(B, L, H, lens, c2p, p2c):
+    ops = _ops()
+    D = 64
+    lens = lens or [L] * B
+    q, k, v, pk, pq = _random(B * 7 + L, (B, L), H, 256, c2p, p2c)
+    sm = oracle.sm_scale_for(D, c2p, p2c)
+    to = lambda t: None if t is None else t.to(DEV)
+    out = ops.disentangled_attention_fp8(to(q), to(k), to(v), to(pk), to(pq), max_seqlen=L, sm_scale=sm,
+                                         seq_lens=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                                         position_buckets=256, max_relative_positions=512)
+    torch.cuda.synchronize()
+    ops.check_status()
+    starts = [b * L for b in range(B)]
+    want, _ = _oracle(q, k, v, pk, pq, starts, lens, sm, 256, 512)
+    fq = lambda x: oracle.fake_quant_e4m3(x.float(), dims=(1, 3))[0].bfloat16()   # per (sequence, head)
+    ft = lambda x: None if x is None else oracle.fake_quant_e4m3(x.float(), dims=(1, 2))[0].bfloat16()  # per head
+    expect, _ = _oracle(fq(q), fq(k), fq(v), ft(pk), ft(pq), starts, lens, sm, 256, 512)
+    got = out.float().cpu().view(-1, H, D)
+    assert torch.isfinite(got).all()
+    d_exp = (got - expect).abs()
+    assert d_exp.max().item() <= FP8_P_MAX and d_exp.mean().item() <= FP8_P_MEAN, (d_exp.max().item(), d_exp.mean().item())
+    d_q = (expect - want).abs()
+    d = (got - want).abs()
+    assert d.max().item() <= 1.5 * d_q.max().item() + FP8_P_MAX
+    assert d.mean().item() <= 1.5 * d_q.mean().item() + FP8_P_MEAN
+    for b, n in enumerate(lens):
+        assert torch.count_nonzero(out[b, n:]) == 0
+
+
+def test_fp8_module_at_deberta_magnitudes():
+    """v3-base attention layer, batch 2 x 512, weights N(0, 0.02): FP8 attention against the fp32 eager module.
+    Stated bound for this configuration: max-abs <= 2e-2, mean-abs <= 3e-3."""
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfAttention
+    from flashdeberta_b200 import FlashDisentangledSelfAttention
+    g = torch.Generator().manual_seed(0)
+    cfg = _Cfg(768, 12, 256, 512, ["c2p", "p2c"], True)
+    eager = DisentangledSelfAttention(cfg).eval()
+    with torch.no_grad():
+        for p in eager.parameters():
+            p.copy_((torch.randn(p.shape, generator=g) * 0.02).bfloat16().float())
+    cfg.attn_fp8 = True
+    flash = FlashDisentangledSelfAttention(cfg).eval()
+    flash.load_state_dict(eager.state_dict())
+    B, L = 2, 512
+    hs = torch.randn(B, L, 768, generator=g).bfloat16().float()
+    rel = (torch.randn(512, 768, generator=g) * 0.02).bfloat16().float()
+    mask = torch.ones(B, L)
+    ext = mask.unsqueeze(1).unsqueeze(2)
+    ext = ext * ext.squeeze(-2).unsqueeze(-1)
+    with torch.no_grad():
+        want = eager.to(DEV)(hs.to(DEV), ext.to(DEV), rel_embeddings=rel.to(DEV))[0].cpu()
+        got = flash.to(DEV).bfloat16()(hs.to(DEV).bfloat16(), mask.to(DEV), rel_embeddings=rel.to(DEV).bfloat16())[0].cpu()
+    _close(got, want, 2e-2, 3e-3, "fp8 module")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
 # errors, model level
 # ---------------------------------------------------------------------------------------------------------------------
 def test_unsupported_inputs_raise():
