@@ -292,6 +292,84 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def varlen_run(args):
+    """Extra measurement (not the headline line): the packed-batch configuration — DeBERTa-v3-large encoder, 256 sequences
+    with log-uniform lengths in [64, 8192] (seed 2, 350907 tokens), bf16, sharded across the ranks by token count with
+    one final gather.  Prints one JSON line with "config": {"workload": "varlen ..."}."""
+    import torch.distributed as dist
+    from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+    from flashdeberta_b200 import ops
+    from flashdeberta_b200.dist import partition_by_tokens
+    from flashdeberta_b200.model import FlashDebertaV2Model
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = DebertaV2Config(
+        vocab_size=128100, hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, intermediate_size=4096,
+        hidden_act="gelu", max_position_embeddings=512, type_vocab_size=0, layer_norm_eps=1e-7, relative_attention=True,
+        max_relative_positions=-1, position_buckets=256, norm_rel_ebd="layer_norm", share_att_key=True,
+        pos_att_type="c2p|p2c", position_biased_input=False, pad_token_id=0)
+    cfg.attn_backend = "b200"
+    torch.manual_seed(2)
+    model = FlashDebertaV2Model(cfg).eval().to(dev).to(torch.bfloat16)
+    g = torch.Generator(device="cpu").manual_seed(2)
+    u = torch.rand(256, dtype=torch.float64, generator=g)
+    lens = torch.floor(torch.exp(math.log(64) + u * (math.log(8192) - math.log(64)))).long().tolist()
+    mine = partition_by_tokens(lens, world)[rank]
+    Lr = max(lens[i] for i in mine)
+    ids = torch.zeros(len(mine), Lr, dtype=torch.long)
+    mask = torch.zeros(len(mine), Lr, dtype=torch.long)
+    for row, i in enumerate(mine):
+        ids[row, : lens[i]] = torch.randint(1, 128100, (lens[i],), generator=g)
+        mask[row, : lens[i]] = 1
+    ids, mask = ids.to(dev), mask.to(dev)
+    my_tokens = sum(lens[i] for i in mine)
+
+    def step():
+        return model(input_ids=ids, attention_mask=mask).last_hidden_state
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            step()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            out = step()
+        t1.record()
+        barrier()
+        ms = t0.elapsed_time(t1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        ops.check_status(dev)
+    total = sum(lens)
+    if rank == 0:
+        f_attn = 24 * attn_flops(lens, heads=16)
+        f_lin = encoder_linear_flops(total, 1024, 4096, 24)
+        print(json.dumps({
+            "metric": "deberta_v3_large_encoder_tokens_per_s", "value": total / (ms / args.steps / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "ms_per_step": ms / args.steps, "scaling": "strong", "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "varlen packed batch, DeBERTa-v3-large encoder, 256 sequences, lengths log-uniform in "
+                                   "[64, 8192] (seed 2)", "total_tokens": total, "tokens_rank0": my_tokens,
+                       "parallelism": f"dp{world}, sequences split by token count"},
+            "model_tflops": (f_attn + f_lin) / (ms / args.steps / 1e3) / 1e12}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -299,8 +377,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--varlen", action="store_true", help="measure the packed v3-large configuration instead")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.varlen:
+        varlen_run(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         gpu_arm(args)

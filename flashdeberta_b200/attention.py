@@ -22,6 +22,39 @@ from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfA
 from . import ops
 
 
+class PackedSequences:
+    """What travels through the layers in place of the attention mask when the encoder runs on packed tokens: the
+    batch is one (1, T, hidden) row of all valid tokens, sequence b owning rows cu_seqlens[b] .. cu_seqlens[b+1]
+    (same role as the (cu_seqlens, max_seqlen) pair of src/flashdeberta/model.py:233-234, made once per model forward
+    instead of once per layer)."""
+
+    def __init__(self, cu_seqlens: torch.Tensor, max_seqlen: int, indices: torch.Tensor, batch: int, seqlen: int):
+        self.cu_seqlens, self.max_seqlen, self.indices = cu_seqlens, int(max_seqlen), indices
+        self.batch, self.seqlen = int(batch), int(seqlen)
+
+    @classmethod
+    def from_mask(cls, mask2d: torch.Tensor) -> "PackedSequences":
+        """One host read (total tokens and longest sequence) per model forward; the reference does one per sequence
+        per layer (src/flashdeberta/ops/flash_attention_varlen.py:71-83) plus one per layer (padding.py:82)."""
+        m = mask2d != 0
+        lens = m.sum(dim=-1, dtype=torch.int32)
+        cu = torch.zeros(lens.numel() + 1, dtype=torch.int32, device=mask2d.device)
+        cu[1:] = torch.cumsum(lens, 0)
+        indices = torch.nonzero(m.flatten(), as_tuple=False).flatten()
+        max_len = int(lens.max().item()) if lens.numel() else 0
+        return cls(cu, max_len, indices, mask2d.shape[0], mask2d.shape[1])
+
+    def pack(self, x: torch.Tensor) -> torch.Tensor:
+        """(B, L, ...) -> (1, T, ...)"""
+        return x.reshape(self.batch * self.seqlen, *x.shape[2:]).index_select(0, self.indices).unsqueeze(0)
+
+    def unpack(self, x: torch.Tensor) -> torch.Tensor:
+        """(1, T, ...) -> (B, L, ...) with zeros in the padding (src/flashdeberta/padding.py:30-44)."""
+        out = x.new_zeros(self.batch * self.seqlen, *x.shape[2:])
+        out.index_copy_(0, self.indices, x[0])
+        return out.view(self.batch, self.seqlen, *x.shape[2:])
+
+
 def lengths_from_mask(attention_mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """Per-sequence valid lengths (int32, on the mask's device) from any of the mask forms the module is handed.
     Returns None for "everything valid".  No host synchronisation."""
@@ -108,6 +141,14 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
 
         if in_dtype != torch.bfloat16:
             q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        if isinstance(attention_mask, PackedSequences):
+            # packed tokens: hidden_states is (1, T, hidden); every sequence is addressed through cu_seqlens
+            pk = attention_mask
+            fn = ops.disentangled_attention_fp8 if self.attn_fp8 else ops.disentangled_attention
+            out = fn(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query, cu_seqlens=pk.cu_seqlens,
+                     max_seqlen=pk.max_seqlen, sm_scale=sm_scale, position_buckets=buckets, max_relative_positions=max_rel)
+            out = out.view(B, L, H * D)
+            return (out if in_dtype == torch.bfloat16 else out.to(in_dtype), None)
         seq_lens = lengths_from_mask(attention_mask)
         if self.attn_fp8:
             out = ops.disentangled_attention_fp8(q, k, v, pos_key, pos_query, seq_lens=seq_lens, max_seqlen=L,

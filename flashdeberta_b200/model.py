@@ -7,6 +7,9 @@ those of transformers, so stock checkpoints load unchanged.  Differences from th
 * the encoder hands every layer the per-sequence lengths (B,) instead of a (B, 1, L, L) mask and never builds the
   (1, L, L) int64 relative-position matrix the flash path ignores (the reference inherits both from
   transformers' encoder forward, src/flashdeberta/model.py:275-310);
+* a batch with padding is packed once after the embeddings, every layer (attention, dense, LayerNorm, FFN) runs on the
+  (1, T, hidden) row of valid tokens, and the result is unpacked once at the end (``config.pack_sequences``, default on;
+  the reference packs and unpacks q, k, v and both bias tensors inside every layer, model.py:216-231, :249);
 * ``config.attn_backend`` chooses the attention core: ``"b200"`` (default, fused kernel) or ``"eager"``
   (transformers' own module).  The reference keys the same switch on ``config._attn_implementation``
   (model.py:254-262), which transformers 5 reserves for its own back-ends.
@@ -33,7 +36,7 @@ from transformers.models.deberta_v2.modeling_deberta_v2 import (
     DisentangledSelfAttention,
 )
 
-from .attention import FlashDisentangledSelfAttention, lengths_from_mask
+from .attention import FlashDisentangledSelfAttention, PackedSequences, lengths_from_mask
 
 __all__ = [
     "DEBERTA_SELF_ATTENTION_CLASSES", "FlashDebertaV2Attention", "FlashDebertaV2Layer", "FlashDebertaV2Encoder",
@@ -75,6 +78,7 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         self.layer = nn.ModuleList([FlashDebertaV2Layer(config) for _ in range(config.num_hidden_layers)])
         self._fused = _backend(config) != "eager"
         self._rel_cache = None
+        self.config_pack = config
 
     def get_rel_embedding(self):
         """LayerNorm(rel_embeddings) does not depend on the input: in eval mode it is computed once and reused, which
@@ -100,6 +104,17 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
             input_mask = attention_mask.sum(-2) > 0
         seq_lens = lengths_from_mask(attention_mask)  # (B,) int32; the only form of the mask the layers see
 
+        # Ragged batch: run the whole stack on packed tokens.  (The convolution of the v2-xlarge models needs the padded
+        # layout, and query_states / a list of hidden states are only used by z_steps: those stay padded.)
+        packed = None
+        if (getattr(self.config_pack, "pack_sequences", True) and self.conv is None and query_states is None
+                and torch.is_tensor(hidden_states) and input_mask.dim() == 2):
+            info = PackedSequences.from_mask(input_mask)
+            if info.indices.numel() < input_mask.numel():
+                packed = info
+        if packed is not None:
+            return self._forward_packed(hidden_states, packed, output_hidden_states, return_dict)
+
         all_hidden_states = (hidden_states,) if output_hidden_states else None
         next_kv = hidden_states
         rel_embeddings = self.get_rel_embedding()
@@ -117,6 +132,20 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
                     next_kv = hidden_states[i + 1] if i + 1 < len(self.layer) else None
             else:
                 next_kv = output_states
+        if not return_dict:
+            return tuple(v for v in [output_states, all_hidden_states, None] if v is not None)
+        return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden_states, attentions=None)
+
+    def _forward_packed(self, hidden_states, packed: PackedSequences, output_hidden_states, return_dict):
+        all_hidden_states = (hidden_states,) if output_hidden_states else None
+        x = packed.pack(hidden_states)  # (1, T, hidden)
+        rel_embeddings = self.get_rel_embedding()
+        for layer_module in self.layer:
+            x, _ = layer_module(x, packed, query_states=None, relative_pos=None, rel_embeddings=rel_embeddings,
+                                output_attentions=False)
+            if output_hidden_states:
+                all_hidden_states = all_hidden_states + (packed.unpack(x),)
+        output_states = all_hidden_states[-1] if output_hidden_states else packed.unpack(x)
         if not return_dict:
             return tuple(v for v in [output_states, all_hidden_states, None] if v is not None)
         return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden_states, attentions=None)
@@ -139,12 +168,40 @@ class FlashDebertaV2Model(DebertaV2Model):
                 token_type_ids: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
                 inputs_embeds: Optional[torch.Tensor] = None, output_attentions: Optional[bool] = None,
                 output_hidden_states: Optional[bool] = None, return_dict: Optional[bool] = None, **kwargs):
-        if self.z_steps > 1 and self.encoder._fused:
+        """Same arguments and outputs as src/flashdeberta/model.py:418-496; the encoder is only asked for every layer's
+        hidden states when the caller wants them (the reference always collects them, model.py:463-467)."""
+        if not self.encoder._fused:
+            return super().forward(input_ids=input_ids, attention_mask=attention_mask, token_type_ids=token_type_ids,
+                                   position_ids=position_ids, inputs_embeds=inputs_embeds,
+                                   output_attentions=output_attentions, output_hidden_states=output_hidden_states,
+                                   return_dict=return_dict, **kwargs)
+        if self.z_steps > 1:
             raise NotImplementedError("z_steps > 1 is not supported with the fused attention backend")
-        return super().forward(input_ids=input_ids, attention_mask=attention_mask, token_type_ids=token_type_ids,
-                               position_ids=position_ids, inputs_embeds=inputs_embeds,
-                               output_attentions=output_attentions, output_hidden_states=output_hidden_states,
-                               return_dict=return_dict, **kwargs)
+        if output_attentions if output_attentions is not None else self.config.output_attentions:
+            raise ValueError("the fused attention never materialises attention probabilities")
+        output_hidden_states = (output_hidden_states if output_hidden_states is not None
+                                else self.config.output_hidden_states)
+        return_dict = return_dict if return_dict is not None else self.config.return_dict
+        if input_ids is not None and inputs_embeds is not None:
+            raise ValueError("You cannot specify both input_ids and inputs_embeds at the same time")
+        if input_ids is not None:
+            input_shape, device = input_ids.size(), input_ids.device
+        elif inputs_embeds is not None:
+            input_shape, device = inputs_embeds.size()[:-1], inputs_embeds.device
+        else:
+            raise ValueError("You have to specify either input_ids or inputs_embeds")
+        if attention_mask is None:
+            attention_mask = torch.ones(input_shape, device=device)
+        if token_type_ids is None:
+            token_type_ids = torch.zeros(input_shape, dtype=torch.long, device=device)
+        embedding_output = self.embeddings(input_ids=input_ids, token_type_ids=token_type_ids,
+                                           position_ids=position_ids, mask=attention_mask, inputs_embeds=inputs_embeds)
+        enc = self.encoder(embedding_output, attention_mask, output_hidden_states=bool(output_hidden_states),
+                           output_attentions=False, return_dict=True)
+        if not return_dict:
+            return (enc.last_hidden_state,) + ((enc.hidden_states,) if output_hidden_states else ())
+        return BaseModelOutput(last_hidden_state=enc.last_hidden_state,
+                               hidden_states=enc.hidden_states if output_hidden_states else None, attentions=None)
 
 
 def _with_flash_backbone(hf_cls, doc):

@@ -435,6 +435,37 @@ def test_fp8_module_at_deberta_magnitudes():
 # ---------------------------------------------------------------------------------------------------------------------
 # errors, model level
 # ---------------------------------------------------------------------------------------------------------------------
+def test_sharded_ragged_batch_matches_whole_batch():
+    """The multi-GPU recipe on one device: split a ragged batch by token count, run each shard on its own, put the
+    results back in order; every sequence must come out as in the whole-batch run (attention bits are identical, the
+    dense layers see a different row count)."""
+    from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+    from flashdeberta_b200 import FlashDebertaV2Model
+    from flashdeberta_b200.dist import gather_sequences, partition_by_tokens, shard_batch
+    torch.manual_seed(1)
+    cfg = DebertaV2Config(vocab_size=500, hidden_size=128, num_hidden_layers=2, num_attention_heads=2,
+                          intermediate_size=256, relative_attention=True, position_buckets=256,
+                          max_relative_positions=512, pos_att_type="c2p|p2c", share_att_key=True,
+                          norm_rel_ebd="layer_norm", position_biased_input=False, type_vocab_size=0)
+    model = FlashDebertaV2Model(cfg).eval().to(DEV).bfloat16()
+    lens = [900, 64, 333, 1200, 65, 700, 128]
+    B, L = len(lens), max(lens)
+    ids = torch.randint(1, 500, (B, L), device=DEV)
+    mask = torch.zeros(B, L, dtype=torch.long, device=DEV)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    with torch.no_grad():
+        whole = model(input_ids=ids, attention_mask=mask).last_hidden_state
+        out = torch.zeros_like(whole)
+        for rank in range(3):
+            sid, smask, owned = shard_batch(ids, mask, rank, 3)
+            assert owned == partition_by_tokens(lens, 3)[rank]
+            h = model(input_ids=sid, attention_mask=smask).last_hidden_state
+            out += gather_sequences(h, owned, B, L)
+    d = (out.float() - whole.float()).abs()
+    assert d.max().item() < 0.1 and d.mean().item() < 5e-3, (d.max().item(), d.mean().item())
+
+
 def test_unsupported_inputs_raise():
     from flashdeberta_b200 import _lib
     ops = _ops()
@@ -483,6 +514,20 @@ def test_model_b200_backend_vs_eager_backend():
     diff = ((got.float() - want) * valid).abs()
     # whole bf16 encoder (LayerNorm output, |x| ~ 1) against the fp32 eager encoder
     assert diff.max().item() < 0.25 and diff.mean().item() < 0.02, (diff.max().item(), diff.mean().item())
+    # the batch above was ragged, so it ran on packed tokens; the padded path must agree with it (same attention kernel
+    # per sequence, GEMMs on a different row count)
+    cfg3 = DebertaV2Config(**{**cfg.to_dict()})
+    cfg3.attn_backend, cfg3.pack_sequences = "b200", False
+    padded = FlashDebertaV2Model(cfg3).eval()
+    padded.load_state_dict(eager.state_dict())
+    padded = padded.to(DEV).bfloat16()
+    with torch.no_grad():
+        got_padded = padded(input_ids=ids, attention_mask=mask, output_hidden_states=True)
+        got_packed = fused(input_ids=ids, attention_mask=mask, output_hidden_states=True)
+    assert len(got_padded.hidden_states) == len(got_packed.hidden_states) == 4
+    d2 = ((got_padded.last_hidden_state.float() - got_packed.last_hidden_state.float()) * valid).abs()
+    assert d2.max().item() < 0.1 and d2.mean().item() < 5e-3, (d2.max().item(), d2.mean().item())
+    assert torch.count_nonzero(got_packed.last_hidden_state * (~valid)) == 0
     head = FlashDebertaV2ForSequenceClassification(cfg2).eval().to(DEV).bfloat16()
     with torch.no_grad():
         logits = head(input_ids=ids, attention_mask=mask).logits
