@@ -33,15 +33,20 @@ class PackedSequences:
         self.batch, self.seqlen = int(batch), int(seqlen)
 
     @classmethod
-    def from_mask(cls, mask2d: torch.Tensor) -> "PackedSequences":
-        """One host read (total tokens and longest sequence) per model forward; the reference does one per sequence
-        per layer (src/flashdeberta/ops/flash_attention_varlen.py:71-83) plus one per layer (padding.py:82)."""
+    def from_mask(cls, mask2d: torch.Tensor) -> Optional["PackedSequences"]:
+        """None when the batch has no padding.  One host read (total tokens and longest sequence) per model forward; the
+        reference does one per sequence per layer (src/flashdeberta/ops/flash_attention_varlen.py:71-83) plus one per
+        layer (padding.py:82)."""
         m = mask2d != 0
         lens = m.sum(dim=-1, dtype=torch.int32)
+        if lens.numel() == 0:
+            return None
+        total, max_len = torch.stack([lens.sum(), lens.max()]).tolist()
+        if total == mask2d.numel():
+            return None
         cu = torch.zeros(lens.numel() + 1, dtype=torch.int32, device=mask2d.device)
         cu[1:] = torch.cumsum(lens, 0)
         indices = torch.nonzero(m.flatten(), as_tuple=False).flatten()
-        max_len = int(lens.max().item()) if lens.numel() else 0
         return cls(cu, max_len, indices, mask2d.shape[0], mask2d.shape[1])
 
     def pack(self, x: torch.Tensor) -> torch.Tensor:

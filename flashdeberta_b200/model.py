@@ -109,9 +109,7 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         packed = None
         if (getattr(self.config_pack, "pack_sequences", True) and self.conv is None and query_states is None
                 and torch.is_tensor(hidden_states) and input_mask.dim() == 2):
-            info = PackedSequences.from_mask(input_mask)
-            if info.indices.numel() < input_mask.numel():
-                packed = info
+            packed = PackedSequences.from_mask(input_mask)
         if packed is not None:
             return self._forward_packed(hidden_states, packed, output_hidden_states, return_dict)
 
