@@ -24,9 +24,10 @@
 //   * saturated tile pair (all distances beyond a saturation point): c2p is one dot product per query row, folded into the
 //     row's exponent offset; p2c is one dot product per key, accumulated into S on the tensor core as R.K^T where all rows
 //     of R equal the saturated pos_query row (R is 8 rows of shared memory read with a zero group stride);
-//   * band tile pair: p2c comes from eight 128x32 products X_q[32(3-b+t) ..].K[32b ..]^T, b = key block, t = 0/1, arranged so
-//     that the value thread (quadrant w, lane l) needs for key 32b+c sits in its own quadrant at lane (l+31-c)&31 of product
-//     t = (l > c): one select on the source side and one warp shuffle per score element, fp32, no shared memory;
+//   * band tile pair: p2c comes from products X_q[32(3-b+t) .. +128).K[32b .. +32)^T, b = key block, t = 0/1 (issued as three
+//     128x64 and two 128x32 MMAs groups), arranged so that the value thread (quadrant w, lane l) needs for key 32b+c sits in
+//     its own quadrant at lane (l+31-c)&31 of product t = (l > c): one select on the source side and one warp shuffle per
+//     score element, fp32, no shared memory;
 //     c2p needs a transpose: X_k[window].Q^T (256x128) is computed into R ahead of the p2c product, the drain group writes it
 //     to shared memory as bf16 [position][query] while the softmax of the previous tile is still running, and thread m
 //     reads c2p[m][m+127-i] at compile-time offsets from a per-thread base.
@@ -394,6 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         };
         const uint32_t idesc_s = instr_desc(128, 128, G::kFmt, 0, 0);
         const uint32_t idesc_p2c = instr_desc(128, 32, G::kFmt, 0, 0);
+        const uint32_t idesc_p2c64 = instr_desc(128, 64, G::kFmt, 0, 0);
         const uint64_t dq = G::desc(smem + kSmemQ, G::kGroup);
         const uint64_t dk0 = G::desc(smem + kSmemK, G::kGroup);
         const uint64_t dwk = G::desc(smem + kSmemWinK, G::kGroup);
@@ -425,19 +427,29 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
             tc_fence_after();
             if (ok && has_p2c) {
-              // product (b, t) = X_q[32(3-b+t) .. +128) . K[32b .. +32)^T  -> 32 columns at R + 32(2b+t)
+              // p2c products.  Key block b (32 keys) needs X_q rows starting at 32(3-b) (t = 0) and 32(4-b) (t = 1); blocks
+              // b and b+1 share the start row 32(3-b), so three 128x64 products cover six of the eight (b, t) pairs and
+              // two 128x32 products the rest (a narrow MMA costs the tensor pipe about as much as a 64-wide one):
+              //   start row 96: keys   0..63  -> R +   0 (b=0,t=0 | b=1,t=1)     start row 128: keys  0..31  -> R + 192 (b=0,t=1)
+              //   start row 64: keys  32..95  -> R +  64 (b=1,t=0 | b=2,t=1)     start row   0: keys 96..127 -> R + 224 (b=3,t=0)
+              //   start row 32: keys  64..127 -> R + 128 (b=2,t=0 | b=3,t=1)
+              const uint64_t blk32 = (32u * G::kRow) >> 4;  // 32 rows of an operand, in descriptor address units
 #pragma unroll 1
-              for (int b = 0; b < 4; ++b) {
-                const uint64_t dkb = dk + uint64_t(b) * ((32u * G::kRow) >> 4);
+              for (int q = 0; q < 3; ++q) {
+                const uint64_t da = dwq + uint64_t(3 - q) * blk32, db = dk + uint64_t(q) * blk32;
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                  const uint64_t dwb = dwq + uint64_t(3 - b + t) * ((32u * G::kRow) >> 4);
-#pragma unroll
-                  for (int ks = 0; ks < G::kSteps; ++ks)
-                    G::mma(tmem_base + kColR + 32 * (2 * b + t), dwb + uint64_t((ks * 32) >> 4),
-                           dkb + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
-                }
+                for (int ks = 0; ks < G::kSteps; ++ks)
+                  G::mma(tmem_base + kColR + 64 * q, da + uint64_t((ks * 32) >> 4), db + uint64_t((ks * 32) >> 4),
+                         idesc_p2c64, ks > 0);
               }
+#pragma unroll
+              for (int ks = 0; ks < G::kSteps; ++ks)
+                G::mma(tmem_base + kColR + 192, dwq + 4 * blk32 + uint64_t((ks * 32) >> 4),
+                       dk + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
+#pragma unroll
+              for (int ks = 0; ks < G::kSteps; ++ks)
+                G::mma(tmem_base + kColR + 224, dwq + uint64_t((ks * 32) >> 4),
+                       dk + 3 * blk32 + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
             }
             ++band_idx;
           } else {
@@ -541,10 +553,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         uint32_t a[32];
         if (ok) tmem_ld32(tmem_lane + kColS + 64 * g + 32 * ch, a);
         if (kind == kBand && has_p2c) {
+          // key block b = 2g + ch: columns of its two products (see the score-issuing warp)
+          const int b = 2 * g + ch;
+          const uint32_t c0 = b == 3 ? 224u : 64u * uint32_t(b);
+          const uint32_t c1 = b == 0 ? 192u : 64u * uint32_t(b) - 32u;
           uint32_t t0[32], t1[32];
           if (ok) {
-            tmem_ld32(tmem_lane + kColR + 32 * (2 * (2 * g + ch)), t0);
-            tmem_ld32(tmem_lane + kColR + 32 * (2 * (2 * g + ch) + 1), t1);
+            tmem_ld32(tmem_lane + kColR + c0, t0);
+            tmem_ld32(tmem_lane + kColR + c1, t1);
             tmem_wait_ld();
           }
 #pragma unroll
