@@ -46,11 +46,13 @@
 #include "internal.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.cuh"
+#include "attn_fwd_common.cuh"
 
 namespace fdb {
 namespace {
 
 using namespace ptx;
+using namespace fwd;
 
 constexpr int kSoftmaxThreads = 256;
 constexpr int kDrainThreads = 128;
@@ -99,121 +101,6 @@ enum Bar : uint32_t {
   kNumBars = 18
 };
 
-struct alignas(64) FwdArgs {
-  CUtensorMap tm_q, tm_k, tm_v, tm_xk, tm_xq;
-  __nv_bfloat16* out;
-  int64_t o_rs, o_hs;
-  const int32_t* seq_info;    // [batch][2] first row, length
-  const int32_t* tile_first;  // [batch+1]
-  const void* xk;             // expanded pos_key   (heads, xrows, 64) bf16 or e4m3
-  const void* xq;             // expanded pos_query
-  const float *q_scale, *k_scale, *v_scale;  // e4m3 only: [seq * heads + head]
-  const float *xk_scale, *xq_scale;          // e4m3 only: [head]
-  float* lse;
-  int32_t* status;
-  int batch, heads, packed, max_seqlen;
-  int sat_lo, sat_hi, d_first, xrows;
-  float scale_log2;  // sm_scale * log2(e)
-#ifdef FDB_TRACE
-  long long* trace;  // [role 0..3][tile 0..63][event 0..7] clock64 stamps of CTA (0, 0)
-#endif
-};
-
-#ifdef FDB_TRACE
-#define FDB_STAMP(role, tile, ev) \
-  do { if (blockIdx.x == 0 && blockIdx.y == 0 && args.trace != nullptr && (tile) < 64) \
-         args.trace[((role) * 64 + (tile)) * 8 + (ev)] = clock64(); } while (0)
-#else
-#define FDB_STAMP(role, tile, ev) do {} while (0)
-#endif
-
-enum TileKind : int { kPlain = 0, kSatHi = 1, kSatLo = 2, kBand = 3 };
-
-// What changes between the bf16 and the e4m3 build of the kernel: bytes per 64-element row (128 / 64, hence 128-byte or
-// 64-byte swizzle and 1024- or 512-byte 8-row groups), elements per MMA along K (16 / 32) and the MMA kind.
-template <bool F8> struct Geo {
-  static constexpr uint32_t kRow = F8 ? 64u : 128u;          // bytes per row of 64 elements
-  static constexpr uint32_t kTile = 128u * kRow;             // a 128-row tile
-  static constexpr uint32_t kWin = 256u * kRow;              // a 256-row window
-  static constexpr uint32_t kGroup = 8u * kRow;              // 8-row group (stride byte offset)
-  static constexpr int kSteps = F8 ? 2 : 4;                  // MMAs along head_dim 64
-  static constexpr int kPvSteps = F8 ? 4 : 8;                // MMAs along 128 keys
-  static constexpr uint32_t kPColsPerStep = 8u;              // TMEM columns of P one P.V MMA reads (16 bf16 / 32 e4m3)
-  static constexpr uint32_t kPCols = F8 ? 16u : 32u;         // TMEM columns of P per softmax group (64 keys)
-  static constexpr int kFmt = F8 ? 0 : 1;                    // instruction-descriptor operand format: e4m3 / bf16
-  __device__ static __forceinline__ uint64_t desc(uint32_t addr, uint32_t group_stride) {
-    return F8 ? smem_desc_sw64(addr, group_stride, 16) : smem_desc_sw128(addr, group_stride, 16);
-  }
-  __device__ static __forceinline__ void mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    if constexpr (F8) mma_f8(d, a, b, idesc, acc); else mma_bf16(d, a, b, idesc, acc);
-  }
-  __device__ static __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    if constexpr (F8) mma_f8_ts(d, a, b, idesc, acc); else mma_bf16_ts(d, a, b, idesc, acc);
-  }
-};
-
-__device__ __forceinline__ float bf16_bits_to_f32(uint32_t v) { return __uint_as_float(v << 16); }
-__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
-  uint16_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
-  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-__device__ __forceinline__ float lds_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-  return v;
-}
-
-// dot product of one query row (128-byte-swizzled in shared memory) with one 64-element bf16 row in global memory
-__device__ __forceinline__ float dot_q_row(uint32_t q_row_addr, int row, const __nv_bfloat16* __restrict__ g) {
-  float acc = 0.f;
-  const uint4* g4 = reinterpret_cast<const uint4*>(g);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {
-    const uint4 a = lds_v4(q_row_addr + (uint32_t((c ^ (row & 7))) << 4));
-    const uint4 b = __ldg(g4 + c);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      acc = fmaf(bf16_bits_to_f32(aw[i] & 0xffffu), bf16_bits_to_f32(bw[i] & 0xffffu), acc);
-      acc = fmaf(bf16_bits_to_f32(aw[i] >> 16), bf16_bits_to_f32(bw[i] >> 16), acc);
-    }
-  }
-  return acc;
-}
-
-// the same for e4m3 rows (64 bytes, 64-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3))
-__device__ __forceinline__ float dot_q_row_f8(uint32_t q_row_addr, int row, const uint8_t* __restrict__ g) {
-  float acc = 0.f;
-  const uint4* g4 = reinterpret_cast<const uint4*>(g);
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const uint4 a = lds_v4(q_row_addr + (uint32_t(c ^ ((row >> 1) & 3)) << 4));
-    const uint4 b = __ldg(g4 + c);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float fa[4], fb[4];
-      unpack_e4m3x4(aw[i], fa);
-      unpack_e4m3x4(bw[i], fb);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) acc = fmaf(fa[k], fb[k], acc);
-    }
-  }
-  return acc;
-}
-
 template <bool F8>
 __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_constant__ FwdArgs args) {
   using G = Geo<F8>;
@@ -251,6 +138,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   const bool has_c2p = args.xk != nullptr, has_p2c = args.xq != nullptr;
   const bool has_pos = has_c2p || has_p2c;
   const int num_kt = (len + kTileN - 1) / kTileN;
+  // key tiles this launch works on: all of them, or (split launch) the contiguous run of band tiles; `jj` counts them
+  int j_first = 0, n_proc = num_kt;
+  if (args.band_only) band_run(m0, num_kt, args.sat_lo, args.sat_hi, j_first, n_proc);
+  const bool resume = args.band_only && n_proc < num_kt;  // the far kernel has left a partial result for this tile
   auto tile_kind = [&](int j) -> int {
     if (!has_pos) return kPlain;
     const int d0 = m0 - j * kTileN - (kTileN - 1);  // smallest distance of the pair; the largest is d0 + 254
@@ -319,7 +210,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       ok = all;
     };
     uint32_t band_idx = 0;
-    for (int j = 0; j < num_kt; ++j) {
+    for (int jj = 0; jj < n_proc; ++jj) {
+      const int j = j_first + jj;
       if (tile_kind(j) != kBand) continue;
       wait(bar(kBarC2p), band_idx & 1u);                               // the product is in R
       if (band_idx > 0) wait(bar(kBarGather), (band_idx - 1u) & 1u);   // nobody reads the previous stage any more
@@ -359,11 +251,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         mbar_expect_tx(bar(kBarQ), G::kTile);
         tma_load_3d(smem + kSmemQ, &args.tm_q, bar(kBarQ), 0, head, seq_row0 + m0);
         int band_idx = 0;
-        for (int j = 0; j < num_kt; ++j) {
-          const int s = j & 1;
-          const uint32_t use = uint32_t(j >> 1);  // how often this stage was used before
+        for (int jj = 0; jj < n_proc && ok; ++jj) {
+          const int j = j_first + jj;
+          const int s = jj & 1;
+          const uint32_t use = uint32_t(jj >> 1);  // how often this stage was used before
           FDB_STAMP(3, j, 0);
-          if (j >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
+          if (jj >= 2) wait(bar(kBarKFree + s), (use - 1u) & 1u);
           if (!ok) break;
           FDB_STAMP(3, j, 1);
           mbar_expect_tx(bar(kBarK + s), G::kTile);
@@ -377,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             if (has_p2c) tma_load_3d(smem + kSmemWinQ, &args.tm_xq, bar(kBarWin), 0, u0, head);
             ++band_idx;
           }
-          if (j >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
+          if (jj >= 2) wait(bar(kBarVFree + s), (use - 1u) & 1u);
           if (!ok) break;
           FDB_STAMP(3, j, 2);
           mbar_expect_tx(bar(kBarV + s), G::kTile);
@@ -404,13 +297,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         int band_idx = 0;
         wait(bar(kBarQ), 0);
 #pragma unroll 1
-        for (int j = 0; j < num_kt; ++j) {
+        for (int jj = 0; jj < n_proc; ++jj) {
+          const int j = j_first + jj;
           const int kind = tile_kind(j);
-          const int s = j & 1;
+          const int s = jj & 1;
           const uint64_t dk = dk0 + uint64_t(s) * (16384u >> 4);  // stages are 16 KB apart in either build
           // both softmax groups hold tile j-1 in registers: S and R are free
-          if (j > 0) wait(bar(kBarSFree), uint32_t(j - 1) & 1u);
-          wait(bar(kBarK + s), uint32_t(j >> 1) & 1u);
+          if (jj > 0) wait(bar(kBarSFree), uint32_t(jj - 1) & 1u);
+          wait(bar(kBarK + s), uint32_t(jj >> 1) & 1u);
           if (kind == kBand) {
             wait(bar(kBarWin), uint32_t(band_idx) & 1u);
             tc_fence_after();
@@ -485,21 +379,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         const uint32_t idesc_pv = instr_desc(128, 64, G::kFmt, 0, 1);
         const uint64_t dv0 = G::desc(smem + kSmemV, G::kGroup);  // V is the MN-major operand: keys run along K
 #pragma unroll 1
-        for (int j = 0; j < num_kt; ++j) {
-          const uint64_t dv = dv0 + uint64_t(j & 1) * (16384u >> 4);
-          wait(bar(kBarV + (j & 1)), uint32_t(j >> 1) & 1u);
-          wait(bar(kBarP), uint32_t(j) & 1u);  // both groups have written P
+        for (int jj = 0; jj < n_proc; ++jj) {
+          const uint64_t dv = dv0 + uint64_t(jj & 1) * (16384u >> 4);
+          wait(bar(kBarV + (jj & 1)), uint32_t(jj >> 1) & 1u);
+          wait(bar(kBarP), uint32_t(jj) & 1u);  // both groups have written P
           tc_fence_after();
-          FDB_STAMP(2, j, 3);
+          FDB_STAMP(2, j_first + jj, 3);
           if (ok) {
 #pragma unroll
             for (int ks = 0; ks < G::kPvSteps; ++ks)  // one step = 2048 bytes of V in either build (16 x 128 B, 32 x 64 B)
               G::mma_ts(tmem_base + kColO, tmem_base + kColP + G::kPColsPerStep * ks, dv + uint64_t((ks * 2048) >> 4),
-                        idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                        idesc_pv, (jj > 0 || ks > 0 || resume) ? 1u : 0u);
           }
           mma_commit(bar(kBarO));
-          mma_commit(bar(kBarVFree + (j & 1)));
-          FDB_STAMP(2, j, 5);
+          mma_commit(bar(kBarVFree + (jj & 1)));
+          FDB_STAMP(2, j_first + jj, 5);
         }
       }
       __syncwarp();  // as above
@@ -536,13 +430,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 
     uint32_t band_idx = 0;
     float m_used = 0.f, l_run = 0.f;
+    if (resume && ok) {
+      // continue from what the far kernel accumulated over the plain and saturated tiles of this row: O goes back into
+      // tensor memory (this group's 32 columns), the reference maximum and the row sum into registers
+      const int64_t rh = (int64_t)(seq_row0 + (my_row < len ? my_row : len - 1)) * args.heads + head;
+      const float4* po = reinterpret_cast<const float4*>(args.part_o + rh * 64 + 32 * g);
+      uint32_t o[32];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 v4 = __ldg(po + q);
+        o[4 * q + 0] = __float_as_uint(v4.x); o[4 * q + 1] = __float_as_uint(v4.y);
+        o[4 * q + 2] = __float_as_uint(v4.z); o[4 * q + 3] = __float_as_uint(v4.w);
+      }
+      tmem_st32(tmem_lane + kColO + 32 * g, o);
+      tmem_wait_st();
+      const float2 ml = __ldg(reinterpret_cast<const float2*>(args.part_ml + rh * 2));
+      m_used = ml.x;
+      l_run = g == 0 ? ml.y : 0.f;
+    }
 
-    for (int j = 0; j < num_kt; ++j) {
+    for (int jj = 0; jj < n_proc; ++jj) {
+      const int j = j_first + jj;
       const int n0 = j * kTileN;
       const int kind = tile_kind(j);
 
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 0);
-      wait(bar(kBarS), uint32_t(j) & 1u);
+      wait(bar(kBarS), uint32_t(jj) & 1u);
       tc_fence_after();
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 1);
 
@@ -614,7 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       for (int i = 4; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the two threads of a row agree on the row maximum
-      const uint32_t xch = smem + kSmemXchg + uint32_t(j & 1) * 1024u;
+      const uint32_t xch = smem + kSmemXchg + uint32_t(jj & 1) * 1024u;
       sts_f32(xch + uint32_t(g) * 512u + uint32_t(r) * 4u, mx);
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 3);
       bar_sync(1, kSoftmaxThreads);
@@ -622,13 +535,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       mx = fmaxf(mx, lds_f32(xch + uint32_t(g ^ 1) * 512u + uint32_t(r) * 4u));
 
       const float t_max = (mx + row_const) * c_eff;
-      if (j == 0) {
+      if (jj == 0 && !resume) {
         m_used = t_max;
       } else {
         // The previous P.V has finished: O may be rescaled and the P columns overwritten.  Observed on every tile (it is
         // long done by now) so that this thread never falls two phases behind the barrier, which a parity wait could
         // not tell apart.
-        wait(bar(kBarO), uint32_t(j - 1) & 1u);
+        if (jj > 0) wait(bar(kBarO), uint32_t(jj - 1) & 1u);
         tc_fence_after();
         // bf16: O is rescaled only when the maximum moved by more than 2^8 (P <= 256 is harmless in bf16).
         // e4m3: P is stored as 2^8 * exp2(.), so it has to stay <= 1: rescale whenever the maximum moves.
@@ -683,7 +596,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     sts_f32(smem + kSmemLsum + uint32_t(g) * 512u + uint32_t(r) * 4u, l_run);
     bar_sync(1, kSoftmaxThreads);
     const float l_tot = l_run + lds_f32(smem + kSmemLsum + uint32_t(g ^ 1) * 512u + uint32_t(r) * 4u);
-    wait(bar(kBarO), uint32_t(num_kt - 1) & 1u);
+    wait(bar(kBarO), uint32_t(n_proc - 1) & 1u);
     tc_fence_after();
     if (ok) {
       const bool valid = my_row < len;
@@ -726,6 +639,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 
 }  // namespace
 
+static bool use_far_for_plain() {
+  const char* env = std::getenv("FDB_ATTN_SPLIT");
+  return !(env != nullptr && env[0] == '0');
+}
+
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream) {
   const bool f8 = p.dtype == FDB_E4M3;
   const char* which = std::getenv("FDB_ATTN_KERNEL");
@@ -751,6 +669,9 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   a.batch = p.batch; a.heads = p.heads; a.packed = p.cu_seqlens != nullptr; a.max_seqlen = p.max_seqlen;
   a.sat_lo = g.sat_lo; a.sat_hi = g.sat_hi; a.d_first = g.d_first; a.xrows = g.rows;
   a.scale_log2 = p.sm_scale * 1.4426950408889634f;
+  a.part_o = w.split ? reinterpret_cast<float*>(ws + w.part_o) : nullptr;
+  a.part_ml = w.split ? reinterpret_cast<float*>(ws + w.part_ml) : nullptr;
+  a.band_only = w.split ? 1 : 0;
 #ifdef FDB_TRACE
   {
     const char* tp = std::getenv("FDB_TRACE_PTR");
@@ -763,6 +684,14 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   if (a.packed) slots = std::min<int64_t>(dense_tiles, (int64_t)(p.total_rows + kTileM - 1) / kTileM + p.batch);
   if (slots <= 0) return FDB_OK;
   if (slots > 2147483647LL || p.heads > 65535) return fail(FDB_ERR_LIMIT, "grid too large");
+
+  // bf16: key tiles with saturated (or no) position terms go to the two-team kernel; with position terms the band tiles
+  // follow in attn_fwd_kernel, which picks up the partial result on the same stream.
+  const bool no_pos = a.xk == nullptr && a.xq == nullptr;
+  if (!f8 && (w.split || (no_pos && use_far_for_plain()))) {
+    if ((rc = launch_attn_fwd_far(&a, slots, p.heads, stream)) != FDB_OK) return rc;
+    if (no_pos) return FDB_OK;
+  }
 
   auto kernel = f8 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);

@@ -55,7 +55,7 @@ extern "C" FDB_API int fdb_attn_fwd_static(const fdb_attn_params* p, void* strea
   if (p->batch == 0 || p->total_rows == 0) return FDB_OK;
   ExpandGeometry g = {0, 0, 0, 0};
   if (p->pos_key != nullptr || p->pos_query != nullptr) g = expand_geometry(p->lut_d_min, p->lut_len);
-  const WorkspaceLayout w = workspace_layout(*p, g);
+  const WorkspaceLayout w = workspace_layout(*p, g, /*allow_split=*/false);  // no room for partial results
   if (w.total > kScratchBytes)
     return fail(FDB_ERR_LIMIT,
                 "these parameters need %llu bytes of scratch, the built-in array holds %llu (FDB_STATIC_SCRATCH_BYTES); "

@@ -10,6 +10,8 @@
 //                      of rows and the fused kernel never evaluates the bucket function.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "internal.h"
 
 namespace fdb {
@@ -27,7 +29,16 @@ ExpandGeometry expand_geometry(int32_t lut_d_min, int32_t lut_len) {
 
 static inline uint64_t align256(uint64_t x) { return (x + 255) & ~uint64_t(255); }
 
-WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry& g) {
+// Two launches pay off once a query tile has key tiles with saturated position terms on both sides of the band.
+static bool want_split(const fdb_attn_params& p) {
+  if (p.dtype == FDB_E4M3 || (p.pos_key == nullptr && p.pos_query == nullptr)) return false;
+  const char* env = std::getenv("FDB_ATTN_SPLIT");
+  if (env != nullptr && env[0] == '0') return false;
+  if (env != nullptr && env[0] == '1') return true;
+  return p.max_seqlen >= 6144;
+}
+
+WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry& g, bool allow_split) {
   WorkspaceLayout w;
   const uint64_t esz = p.dtype == FDB_E4M3 ? 1 : 2;
   uint64_t off = 0;
@@ -36,6 +47,10 @@ WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry&
   const uint64_t table = uint64_t(p.heads) * g.rows * kHeadDim * esz;
   w.exp_key = off;    off = align256(off + (p.pos_key ? table : 0));
   w.exp_query = off;  off = align256(off + (p.pos_query ? table : 0));
+  w.split = allow_split && want_split(p);
+  const uint64_t cells = w.split ? uint64_t(p.total_rows) * p.heads : 0;
+  w.part_o = off;     off = align256(off + cells * kHeadDim * sizeof(float));
+  w.part_ml = off;    off = align256(off + cells * 2 * sizeof(float));
   w.total = off;
   return w;
 }

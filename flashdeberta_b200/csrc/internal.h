@@ -42,15 +42,20 @@ struct WorkspaceLayout {
   uint64_t tile_first; // int32[batch+1] exclusive prefix of ceil(len/kTileM)
   uint64_t exp_key;    // expanded pos_key, (heads, rows, 64) elements of the input type
   uint64_t exp_query;  // expanded pos_query
+  uint64_t part_o;     // split launch only: float (total_rows, heads, 64) unnormalised output of the far key tiles
+  uint64_t part_ml;    // split launch only: float (total_rows, heads, 2) reference maximum (log2 units), row sum
+  bool split;          // far key tiles and band key tiles run as two launches
   uint64_t total;
 };
-WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry& g);
+// `allow_split` false keeps every key tile in one launch (no partial-result buffers in the workspace).
+WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry& g, bool allow_split = true);
 
 // ---- launchers (defined in the .cu files) --------------------------------------------------------------------------
 int launch_attn_check(const fdb_attn_params& p, void* stream);
 int launch_prepare(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
 int launch_attn_fwd_serial(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
+int launch_attn_fwd_far(const void* fwd_args, int64_t slots, int heads, void* stream);  // fwd_args: fwd::FwdArgs
 int launch_relative_index_matrix(const int16_t* lut, int32_t d_min, int32_t len, int32_t lq, int32_t lk, int32_t* out,
                                  void* stream);
 int launch_quantize_e4m3(const void* x, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,

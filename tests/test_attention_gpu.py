@@ -261,6 +261,68 @@ def test_fused_position_variants(c2p, p2c, buckets, max_rel):
     _close(out.view(-1, H, D), want, BF16_MAX, BF16_MEAN)
 
 
+@pytest.mark.parametrize("c2p,p2c", [(True, True), (True, False), (False, True)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c, packed):
+    """Sequences long enough to have saturated key tiles on both sides of the band, run with the far key tiles in the
+    two-team kernel and the band tiles in a second launch (forced through FDB_ATTN_SPLIT, which the library reads on
+    every call; long calls take this path by themselves), against the single launch and the CPU oracle."""
+    ops = _ops()
+    H, D, buckets, max_rel = 2, 64, 256, 512
+    lens = [1900, 130, 1, 1409, 2048]
+    L = max(lens)
+    sm = oracle.sm_scale_for(D, c2p, p2c)
+    if packed:
+        q, k, v, pk, pq = _random(11, (sum(lens),), H, 256, c2p, p2c)
+        cu = [0]
+        for n in lens:
+            cu.append(cu[-1] + n)
+        starts = cu[:-1]
+        kw = dict(cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV), max_seqlen=L)
+    else:
+        q, k, v, pk, pq = _random(12, (len(lens), L), H, 256, c2p, p2c)
+        starts = [b * L for b in range(len(lens))]
+        kw = dict(seq_lens=torch.tensor(lens, dtype=torch.int32, device=DEV), max_seqlen=L)
+    to = lambda t: None if t is None else t.to(DEV)
+    args = (to(q), to(k), to(v), to(pk), to(pq))
+    kw.update(sm_scale=sm, position_buckets=buckets, max_relative_positions=max_rel, return_lse=True)
+    monkeypatch.setenv("FDB_ATTN_SPLIT", "1")
+    out2, lse2 = ops.disentangled_attention(*args, **kw)
+    monkeypatch.setenv("FDB_ATTN_SPLIT", "0")
+    out1, lse1 = ops.disentangled_attention(*args, **kw)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want, want_lse = _oracle(q, k, v, pk, pq, starts, lens, sm, buckets, max_rel)
+    _close(out2.view(-1, H, D), want, BF16_MAX, BF16_MEAN, "two launches")
+    _close(out1.view(-1, H, D), want, BF16_MAX, BF16_MEAN, "one launch")
+    assert (lse2.cpu() - want_lse).abs().max().item() < 2e-2
+    assert (lse2 - lse1).abs().max().item() < 2e-2
+    if not packed:  # padding rows are zero on either path
+        for b, n in enumerate(lens):
+            assert torch.count_nonzero(out2[b, n:]) == 0
+
+
+@pytest.mark.parametrize("lens", [[1], [128], [129], [300, 129, 7], [1000, 1000], [2050, 1, 1279]])
+def test_position_free_ragged_lengths(lens):
+    """No position terms at all (plain softmax attention): every key tile goes through the two-team kernel."""
+    ops = _ops()
+    H, D = 2, 64
+    q, k, v, _, _ = _random(21 + len(lens), (sum(lens),), H, 1, False, False)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    sm = oracle.sm_scale_for(D, False, False)
+    to = lambda t: t.to(DEV)
+    out, lse = ops.disentangled_attention(to(q), to(k), to(v), None, None, sm_scale=sm, position_buckets=-1,
+                                          max_relative_positions=-1, return_lse=True, max_seqlen=max(lens),
+                                          cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV))
+    torch.cuda.synchronize()
+    ops.check_status()
+    want, want_lse = _oracle(q, k, v, None, None, cu[:-1], lens, sm, -1, -1)
+    _close(out.view(-1, H, D), want, BF16_MAX, BF16_MEAN, str(lens))
+    assert (lse.cpu() - want_lse).abs().max().item() < 2e-2
+
+
 def test_packed_equals_dense_bitwise_and_order_does_not_matter():
     """Each sequence is computed by the same tiles whatever the batch layout: packed, padded and permuted batches give
     identical bits (the property the multi-GPU sharding relies on)."""
