@@ -217,21 +217,28 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       if (band_idx > 0) wait(bar(kBarGather), (band_idx - 1u) & 1u);   // nobody reads the previous stage any more
       tc_fence_after();
       if (has_c2p && ok) {
+        // The windows of consecutive band tiles overlap by half: only the first tile of the run brings 256 positions,
+        // every later one the 128 new ones (block 0), written over the half of the stage the new window no longer
+        // covers.  Position p of the current window sits in stage row p ^ flip.
+        const int nblk = band_idx == 0 ? 2 : 1;
+        const uint32_t flip = (band_idx & 1u) ? 128u : 0u;
 #pragma unroll 1
-        for (int blk = 0; blk < 2; ++blk) {
-          const uint32_t row_addr = smem + kSmemStageC + uint32_t(blk * 128 + r) * kStageCPitch;
-#pragma unroll 1
+        for (int blk = 0; blk < nblk; ++blk) {
+          const uint32_t row_addr = smem + kSmemStageC + (uint32_t(blk * 128 + r) ^ flip) * kStageCPitch;
+          const uint32_t col = tmem_lane + kColR + blk * 128;
+          uint32_t t[32];
+          tmem_ld32(col, t);
+          tmem_wait_ld();
+#pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t t[32];
-            tmem_ld32(tmem_lane + kColR + blk * 128 + c4 * 32, t);
-            tmem_wait_ld();
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(t[2 * i]), __uint_as_float(t[2 * i + 1]));
+            if (c4 < 3) tmem_ld32(col + (c4 + 1) * 32, t);  // the next 32 columns are in flight while these are stored
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4)
-              sts_v4(row_addr + (c4 * 4 + q4) * 16,
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 0]), __uint_as_float(t[q4 * 8 + 1])),
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 2]), __uint_as_float(t[q4 * 8 + 3])),
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 4]), __uint_as_float(t[q4 * 8 + 5])),
-                     pack_bf16x2(__uint_as_float(t[q4 * 8 + 6]), __uint_as_float(t[q4 * 8 + 7])));
+              sts_v4(row_addr + (c4 * 4 + q4) * 16, pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+            if (c4 < 3) tmem_wait_ld();
           }
         }
       }
@@ -309,15 +316,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             wait(bar(kBarWin), uint32_t(band_idx) & 1u);
             tc_fence_after();
             if (ok && has_c2p) {
-              // c2pT[p][m] = X_k[p].Q[m]: two 128-position blocks -> R columns [0,128) and [128,256)
-#pragma unroll
-              for (int blk = 0; blk < 2; ++blk)
+              // c2pT[p][m] = X_k[p].Q[m] in 128-position blocks -> R columns [0,128) (and [128,256) on the first tile of
+              // the run; later tiles reuse the lower half of the previous window from the stage)
+              const int nblk = band_idx == 0 ? 2 : 1;
+#pragma unroll 1
+              for (int blk = 0; blk < nblk; ++blk)
 #pragma unroll
                 for (int ks = 0; ks < G::kSteps; ++ks)
                   G::mma(tmem_base + kColR + blk * 128, dwk + uint64_t((blk * G::kTile + ks * 32) >> 4),
                          dq + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             }
             mma_commit(bar(kBarC2p));
+            if (ok) {  // the scores do not need R: they are computed while the drain group empties it
+#pragma unroll
+              for (int ks = 0; ks < G::kSteps; ++ks)
+                G::mma(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
+            }
             wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
             tc_fence_after();
             if (ok && has_p2c) {
@@ -349,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           } else {
             tc_fence_after();
           }
-          if (ok) {
+          if (ok && kind != kBand) {
 #pragma unroll
             for (int ks = 0; ks < G::kSteps; ++ks)
               G::mma(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
@@ -505,10 +519,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       if (kind == kBand) {
         wait(bar(kBarStage), band_idx & 1u);  // the c2p stage of this tile is complete
         if (has_c2p) {
-          // c2p[m][i] sits at stage[(m + 127 - i)][m]
+          // c2p[m][i] is position p = m + 127 - i of the window, query column m; position p sits in stage row p ^ flip
+          // (see the drain group): 128 rows up for the new half (p < 128 <=> i >= m), 128 rows down for the kept one
           const uint32_t base = smem + kSmemStageC + uint32_t(r + 127 - 64 * g) * kStageCPitch + uint32_t(r) * 2u;
+          const uint32_t fl = (band_idx & 1u) ? 128u * kStageCPitch : 0u;
+          const uint32_t base_new = base + fl, base_old = base - fl;
+          const int thr = r - 64 * g;
 #pragma unroll
-          for (int i = 0; i < 64; ++i) s[i] = fmaf(bf16_bits_to_f32(lds_u16(base - uint32_t(i) * kStageCPitch)), ratio_c, s[i]);
+          for (int i = 0; i < 64; ++i)
+            s[i] = fmaf(bf16_bits_to_f32(lds_u16((i >= thr ? base_new : base_old) - uint32_t(i) * kStageCPitch)), ratio_c, s[i]);
         }
         mbar_arrive(bar(kBarGather));
         ++band_idx;
