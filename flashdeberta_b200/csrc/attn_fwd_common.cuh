@@ -16,10 +16,12 @@ using namespace ptx;
 
 struct alignas(64) FwdArgs {
   CUtensorMap tm_q, tm_k, tm_v, tm_xk, tm_xq;
+  CUtensorMap tm_xq_sat;      // expanded pos_query again, 8-row boxes: the saturated rows as an MMA operand
   __nv_bfloat16* out;
   int64_t o_rs, o_hs;
   const int32_t* seq_info;    // [batch][2] first row, length
   const int32_t* tile_first;  // [batch+1]
+  const int4* slot_info;      // [slots] (sequence, first query row of the tile within it, sequence's first row, length); sequence < 0: empty slot
   const void* xk;             // expanded pos_key   (heads, xrows, 64) bf16 or e4m3
   const void* xq;             // expanded pos_query
   const float *q_scale, *k_scale, *v_scale;  // e4m3 only: [seq * heads + head]
@@ -34,6 +36,7 @@ struct alignas(64) FwdArgs {
   float* part_o;   // (rows, heads, 64)
   float* part_ml;  // (rows, heads, 2)
   int band_only;   // attn_fwd_kernel: 0 = every key tile, 1 = band tiles only (continuing from part_o / part_ml)
+  int slots;       // query-tile slots of the launch (work items = slots * heads)
 #ifdef FDB_TRACE
   long long* trace;  // [role 0..3][tile 0..63][event 0..7] clock64 stamps of CTA (0, 0)
 #endif

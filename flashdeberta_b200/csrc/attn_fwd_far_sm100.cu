@@ -71,17 +71,10 @@ __global__ void __launch_bounds__(kFarThreads, 1) attn_fwd_far_kernel(const __gr
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int head = blockIdx.y;
 
-  const int tile = blockIdx.x;
-  if (tile >= __ldg(args.tile_first + args.batch)) return;
-  int lo = 0, hi = args.batch;
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (__ldg(args.tile_first + mid) <= tile) lo = mid; else hi = mid;
-  }
-  const int seq = lo;
-  const int m0 = (tile - __ldg(args.tile_first + seq)) * kTileM;
-  const int seq_row0 = __ldg(args.seq_info + 2 * seq);
-  const int len = __ldg(args.seq_info + 2 * seq + 1);
+  const int4 slot = __ldg(args.slot_info + blockIdx.x);  // (sequence, first row of the tile in it, its first row, its length)
+  if (slot.x < 0) return;                                  // slot past the last sequence
+  const int seq = slot.x, m0 = slot.y, seq_row0 = slot.z, len = slot.w;
+  (void)seq;
   const int row_limit = args.packed ? len : args.max_seqlen;
   const bool has_c2p = args.xk != nullptr, has_p2c = args.xq != nullptr;
   const bool has_pos = has_c2p || has_p2c;
@@ -118,14 +111,6 @@ __global__ void __launch_bounds__(kFarThreads, 1) attn_fwd_far_kernel(const __gr
     }
     fence_barrier_init();
   }
-  if (has_p2c && tid < 128) {
-    const int t = tid >> 6, row = (tid >> 3) & 7, c = tid & 7;
-    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(args.xq) +
-                               ((int64_t)head * args.xrows + (t == 0 ? args.xrows - 1 : 0)) * kHeadDim;
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + c);
-    sts_v4(smem + kFSmemSat + t * 1024 + row * 128 + (uint32_t(c ^ row) << 4), v.x, v.y, v.z, v.w);
-    fence_proxy_async_smem();
-  }
   if (warp == kFarScoreWarp) {
     tmem_alloc(tmem_slot, kFarTmemCols);
     tmem_relinquish();
@@ -145,8 +130,14 @@ __global__ void __launch_bounds__(kFarThreads, 1) attn_fwd_far_kernel(const __gr
     if (warp == kFarTmaWarp) {
       if (lane == 0) {
         tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
-        mbar_expect_tx(bar(kFBarQ), 16384);
+        mbar_expect_tx(bar(kFBarQ), 16384u + (has_p2c ? 2048u : 0u));
         tma_load_3d(smem + kFSmemQ, &args.tm_q, bar(kFBarQ), 0, head, seq_row0 + m0);
+        if (has_p2c) {
+          // Saturated pos_query rows as MMA operands: the last (first) eight rows of an expanded table are all the row of
+          // distances beyond sat_hi (sat_lo), so an 8-row box is the 8 identical rows in the swizzled layout.
+          tma_load_3d(smem + kFSmemSat, &args.tm_xq_sat, bar(kFBarQ), 0, args.xrows - 8, head);
+          tma_load_3d(smem + kFSmemSat + 1024, &args.tm_xq_sat, bar(kFBarQ), 0, 0, head);
+        }
 #pragma unroll 1
         for (int i = 0; i < n_far; ++i) {
           const int st = i % kStages;

@@ -84,7 +84,7 @@ static_assert(kSmemBytes <= 232448, "exceeds 227 KB");
 
 // mbarriers.  "count" = arrivals per phase.
 enum Bar : uint32_t {
-  kBarQ = 0,         // 1   Q landed (TMA)
+  kBarQ = 0,         // 1   Q (and the saturated pos_query rows of the head) landed (TMA)
   kBarK = 1,         // 1   K stage s landed (TMA), 2 stages
   kBarV = 3,         // 1   V stage s landed (TMA), 2 stages
   kBarKFree = 5,     // 1   the MMAs that read K stage s finished (tcgen05.commit)
@@ -111,17 +111,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   const int head = blockIdx.y;
 
   // ---- which tile ------------------------------------------------------------------------------------------------
-  const int tile = blockIdx.x;
-  if (tile >= __ldg(args.tile_first + args.batch)) return;
-  int lo = 0, hi = args.batch;
-  while (hi - lo > 1) {  // largest b with tile_first[b] <= tile
-    const int mid = (lo + hi) >> 1;
-    if (__ldg(args.tile_first + mid) <= tile) lo = mid; else hi = mid;
-  }
-  const int seq = lo;
-  const int m0 = (tile - __ldg(args.tile_first + seq)) * kTileM;
-  const int seq_row0 = __ldg(args.seq_info + 2 * seq);
-  const int len = __ldg(args.seq_info + 2 * seq + 1);
+  const int4 slot = __ldg(args.slot_info + blockIdx.x);  // (sequence, first row of the tile in it, its first row, its length)
+  if (slot.x < 0) return;                                  // slot past the last sequence
+  const int seq = slot.x, m0 = slot.y, seq_row0 = slot.z, len = slot.w;
   // rows of this tile that may be written: packed -> the sequence's own rows; dense -> the padded row range
   const int row_limit = args.packed ? len : args.max_seqlen;
 
@@ -162,18 +154,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
-  }
-  if (has_p2c && tid < 128) {
-    // saturated pos_query rows, 8 identical rows each, in the swizzled operand layout: tile 0 = last row, 1 = first
-    const int t = tid >> 6, row = (tid >> 3) & 7, c = tid & 7;
-    const uint8_t* src = static_cast<const uint8_t*>(args.xq) +
-                         ((int64_t)head * args.xrows + (t == 0 ? args.xrows - 1 : 0)) * G::kRow;
-    if (c < int(G::kRow / 16)) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + c);
-      const uint32_t sw = F8 ? uint32_t(c ^ ((row >> 1) & 3)) : uint32_t(c ^ row);
-      sts_v4(smem + kSmemSat + t * 1024 + row * G::kRow + (sw << 4), v.x, v.y, v.z, v.w);
-    }
-    fence_proxy_async_smem();
   }
   // e4m3: value = stored * scale.  The three score terms carry different scale products; they are brought to the one of
   // Q.K^T (ratio_c, ratio_p) when they are added, and that product goes into the softmax scale.
@@ -255,8 +235,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           if (ok && !mbar_wait_abortable(b, parity, abort_flag)) { ok = false; *abort_flag = 1u; }
         };
         tma_prefetch_desc(&args.tm_q); tma_prefetch_desc(&args.tm_k); tma_prefetch_desc(&args.tm_v);
-        mbar_expect_tx(bar(kBarQ), G::kTile);
+        mbar_expect_tx(bar(kBarQ), G::kTile + (has_p2c ? 16u * G::kRow : 0u));
         tma_load_3d(smem + kSmemQ, &args.tm_q, bar(kBarQ), 0, head, seq_row0 + m0);
+        if (has_p2c) {
+          // Saturated pos_query rows as MMA operands: the last (first) eight rows of an expanded table are all the row of
+          // distances beyond sat_hi (sat_lo), so an 8-row box is the 8 identical rows in the swizzled layout.
+          tma_load_3d(smem + kSmemSat, &args.tm_xq_sat, bar(kBarQ), 0, args.xrows - 8, head);
+          tma_load_3d(smem + kSmemSat + 1024, &args.tm_xq_sat, bar(kBarQ), 0, 0, head);
+        }
         int band_idx = 0;
         for (int jj = 0; jj < n_proc && ok; ++jj) {
           const int j = j_first + jj;
@@ -680,10 +666,12 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   // a map is always encoded so the kernel argument is well formed; an unused one points at q
   if (a.xk) { if ((rc = make_map_table(&a.tm_xk, a.xk, g.rows, p.heads, f8, "expanded pos_key"))) return rc; } else a.tm_xk = a.tm_q;
   if (a.xq) { if ((rc = make_map_table(&a.tm_xq, a.xq, g.rows, p.heads, f8, "expanded pos_query"))) return rc; } else a.tm_xq = a.tm_q;
+  if (a.xq) { if ((rc = make_map_table(&a.tm_xq_sat, a.xq, g.rows, p.heads, f8, "saturated pos_query rows", 8))) return rc; } else a.tm_xq_sat = a.tm_q;
   a.out = static_cast<__nv_bfloat16*>(p.out);
   a.o_rs = p.out_row_stride; a.o_hs = p.out_head_stride;
   a.seq_info = reinterpret_cast<const int32_t*>(ws + w.seq_info);
   a.tile_first = reinterpret_cast<const int32_t*>(ws + w.tile_first);
+  a.slot_info = reinterpret_cast<const int4*>(ws + w.slot_info);
   a.lse = p.lse; a.status = p.status;
   a.batch = p.batch; a.heads = p.heads; a.packed = p.cu_seqlens != nullptr; a.max_seqlen = p.max_seqlen;
   a.sat_lo = g.sat_lo; a.sat_hi = g.sat_hi; a.d_first = g.d_first; a.xrows = g.rows;
@@ -698,9 +686,8 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   }
 #endif
 
-  const int64_t dense_tiles = (int64_t)p.batch * ((p.max_seqlen + kTileM - 1) / kTileM);
-  int64_t slots = dense_tiles;
-  if (a.packed) slots = std::min<int64_t>(dense_tiles, (int64_t)(p.total_rows + kTileM - 1) / kTileM + p.batch);
+  const int64_t slots = tile_slots(p);
+  a.slots = (int)slots;
   if (slots <= 0) return FDB_OK;
   if (slots > 2147483647LL || p.heads > 65535) return fail(FDB_ERR_LIMIT, "grid too large");
 

@@ -38,12 +38,20 @@ static bool want_split(const fdb_attn_params& p) {
   return p.max_seqlen >= 6144;
 }
 
+int64_t tile_slots(const fdb_attn_params& p) {
+  const int64_t dense_tiles = (int64_t)p.batch * ((p.max_seqlen + kTileM - 1) / kTileM);
+  if (p.cu_seqlens == nullptr) return dense_tiles;
+  const int64_t bound = (int64_t)(p.total_rows + kTileM - 1) / kTileM + p.batch;
+  return dense_tiles < bound ? dense_tiles : bound;
+}
+
 WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry& g, bool allow_split) {
   WorkspaceLayout w;
   const uint64_t esz = p.dtype == FDB_E4M3 ? 1 : 2;
   uint64_t off = 0;
   w.seq_info = off;   off = align256(off + uint64_t(p.batch) * 2 * sizeof(int32_t));
   w.tile_first = off; off = align256(off + uint64_t(p.batch + 1) * sizeof(int32_t));
+  w.slot_info = off;  off = align256(off + uint64_t(tile_slots(p)) * 4 * sizeof(int32_t));
   const uint64_t table = uint64_t(p.heads) * g.rows * kHeadDim * esz;
   w.exp_key = off;    off = align256(off + (p.pos_key ? table : 0));
   w.exp_query = off;  off = align256(off + (p.pos_query ? table : 0));
@@ -64,6 +72,7 @@ __global__ void __launch_bounds__(kScanThreads) seq_info_kernel(const int32_t* _
                                                                 int max_seqlen, int total_rows,
                                                                 int32_t* __restrict__ seq_info,
                                                                 int32_t* __restrict__ tile_first,
+                                                                int4* __restrict__ slot_info, int slots,
                                                                 int32_t* __restrict__ status) {
   __shared__ int32_t partial[kScanThreads];
   const int t = threadIdx.x;
@@ -100,9 +109,13 @@ __global__ void __launch_bounds__(kScanThreads) seq_info_kernel(const int32_t* _
   int32_t run = partial[t] - sum;  // exclusive
   for (int b = b0; b < b1; ++b) {
     tile_first[b] = run;
-    run += packed ? (seq_info[2 * b + 1] + kTileM - 1) / kTileM : dense_tiles;
+    const int start = seq_info[2 * b], len = seq_info[2 * b + 1];
+    const int tiles = packed ? (len + kTileM - 1) / kTileM : dense_tiles;
+    for (int i = 0; i < tiles && run + i < slots; ++i) slot_info[run + i] = make_int4(b, i * kTileM, start, len);
+    run += tiles;
   }
   if (t == kScanThreads - 1) tile_first[batch] = partial[t];
+  for (int i = partial[kScanThreads - 1] + t; i < slots; i += kScanThreads) slot_info[i] = make_int4(-1, 0, 0, 0);
   if (bad && status != nullptr) atomicOr(reinterpret_cast<unsigned int*>(status), FDB_DEV_BAD_SEQLEN);
 }
 
@@ -132,7 +145,8 @@ int launch_prepare(const fdb_attn_params& p, const ExpandGeometry& g, const Work
   char* ws = static_cast<char*>(p.workspace);
   seq_info_kernel<<<1, kScanThreads, 0, s>>>(p.cu_seqlens, p.seq_lens, p.batch, p.max_seqlen, p.total_rows,
                                              reinterpret_cast<int32_t*>(ws + w.seq_info),
-                                             reinterpret_cast<int32_t*>(ws + w.tile_first), p.status);
+                                             reinterpret_cast<int32_t*>(ws + w.tile_first),
+                                             reinterpret_cast<int4*>(ws + w.slot_info), (int)tile_slots(p), p.status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "seq_info launch: %s", cudaGetErrorString(e));
   if (p.pos_key != nullptr || p.pos_query != nullptr) {

@@ -40,6 +40,8 @@ ExpandGeometry expand_geometry(int32_t lut_d_min, int32_t lut_len);
 struct WorkspaceLayout {
   uint64_t seq_info;   // int32[batch][2] first row, length
   uint64_t tile_first; // int32[batch+1] exclusive prefix of ceil(len/kTileM)
+  uint64_t slot_info;  // int32[slots][4] per query-tile slot: sequence (-1: unused slot), first row within it, the
+                       // sequence's first row, its length
   uint64_t exp_key;    // expanded pos_key, (heads, rows, 64) elements of the input type
   uint64_t exp_query;  // expanded pos_query
   uint64_t part_o;     // split launch only: float (total_rows, heads, 64) unnormalised output of the far key tiles
@@ -49,6 +51,9 @@ struct WorkspaceLayout {
 };
 // `allow_split` false keeps every key tile in one launch (no partial-result buffers in the workspace).
 WorkspaceLayout workspace_layout(const fdb_attn_params& p, const ExpandGeometry& g, bool allow_split = true);
+// Query-tile slots of a call: dense -> every tile of the padded row range; packed -> an upper bound on the tiles of the
+// sequences (the exact number is only known on the device).
+int64_t tile_slots(const fdb_attn_params& p);
 
 // ---- launchers (defined in the .cu files) --------------------------------------------------------------------------
 int launch_attn_check(const fdb_attn_params& p, void* stream);

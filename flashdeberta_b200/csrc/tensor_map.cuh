@@ -45,13 +45,14 @@ inline int make_map_rows(CUtensorMap* m, const void* base, int64_t rows, int hea
 }
 
 // expanded table (heads, xrows, 64) contiguous -> 3-D map (d, row, head), box 64 x 256 x 1
-inline int make_map_table(CUtensorMap* m, const void* base, int xrows, int heads, bool f8, const char* what) {
+inline int make_map_table(CUtensorMap* m, const void* base, int xrows, int heads, bool f8, const char* what,
+                          int box_rows = kWindow) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return fail(FDB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   const cuuint64_t row = f8 ? 64 : 128;
   const cuuint64_t dims[3] = {64, (cuuint64_t)xrows, (cuuint64_t)heads};
   const cuuint64_t strides[2] = {row, (cuuint64_t)xrows * row};
-  const cuuint32_t box[3] = {64, (cuuint32_t)kWindow, 1};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(m, f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
