@@ -527,10 +527,14 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 #pragma unroll
         for (int i = 0; i < 64; ++i) s[i] = i < valid ? s[i] : -INFINITY;
       }
-      float mx4[4] = {s[0], s[1], s[2], s[3]};
+      float mx4[4] = {max3(s[0], s[4], s[8]), max3(s[1], s[5], s[9]), max3(s[2], s[6], s[10]), max3(s[3], s[7], s[11])};
 #pragma unroll
-      for (int i = 4; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      for (int i = 12; i < 60; i += 8)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) mx4[q] = max3(mx4[q], s[i + q], s[i + 4 + q]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], s[60 + q]);
+      float mx = max3(mx4[0], mx4[1], fmaxf(mx4[2], mx4[3]));
       // the two threads of a row agree on the row maximum
       const uint32_t xch = smem + kSmemXchg + uint32_t(jj & 1) * 1024u;
       sts_f32(xch + uint32_t(g) * 512u + uint32_t(r) * 4u, mx);
@@ -569,27 +573,48 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       }
       if (lane == 0 && quad == 0) FDB_STAMP(g, j, 5);
       const float off = row_const * c_eff - m_used + (F8 ? 8.f : 0.f);
-      float l4[4] = {0.f, 0.f, 0.f, 0.f};
+      if constexpr (F8) {
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        s[i] = ex2(fmaf(s[i], c_eff, off));
-        l4[i & 3] += s[i];
-      }
-      l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-      if (lane == 0 && quad == 0) FDB_STAMP(g, j, 6);
-      // P for this group's 64 keys: 32 columns of bf16 pairs, or 16 columns of e4m3 quadruples
-      if (ok) {
-        if constexpr (F8) {
+        for (int i = 0; i < 64; ++i) {
+          s[i] = ex2(fmaf(s[i], c_eff, off));
+          l4[i & 3] += s[i];
+        }
+        l_run += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+        if (lane == 0 && quad == 0) FDB_STAMP(g, j, 6);
+        if (ok) {  // 16 columns of e4m3 quadruples
           uint32_t p[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) p[i] = pack_e4m3x4(s[4 * i], s[4 * i + 1], s[4 * i + 2], s[4 * i + 3]);
           tmem_st16(tmem_lane + kColP + 16 * g, p);
-        } else {
-          uint32_t p[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) p[i] = pack_bf16x2(s[2 * i], s[2 * i + 1]);
-          tmem_st32(tmem_lane + kColP + 32 * g, p);
+          tmem_wait_st();
         }
+      } else {
+        // p = 2^(s * scale + off) with the two-wide fp32 forms; the bf16 pairs of the first 32 keys are on their way to
+        // tensor memory while the other 32 are computed
+        const uint64_t scale2 = pack_f32x2(c_eff, c_eff), off2 = pack_f32x2(off, off);
+        uint64_t l2[2] = {0ull, 0ull};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t p[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float e0, e1, e2, e3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(s[32 * h + i], s[32 * h + i + 1]), scale2, off2), e0, e1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(s[32 * h + i + 2], s[32 * h + i + 3]), scale2, off2), e2, e3);
+            e0 = ex2(e0); e1 = ex2(e1); e2 = ex2(e2); e3 = ex2(e3);
+            l2[0] = add_f32x2(l2[0], pack_f32x2(e0, e1));
+            l2[1] = add_f32x2(l2[1], pack_f32x2(e2, e3));
+            p[i >> 1] = pack_bf16x2(e0, e1);
+            p[(i >> 1) + 1] = pack_bf16x2(e2, e3);
+          }
+          if (ok) tmem_st16(tmem_lane + kColP + 32 * g + 16 * h, p);
+        }
+        float s0, s1, s2, s3;
+        unpack_f32x2(l2[0], s0, s1);
+        unpack_f32x2(l2[1], s2, s3);
+        l_run += (s0 + s1) + (s2 + s3);
+        if (lane == 0 && quad == 0) FDB_STAMP(g, j, 6);
         tmem_wait_st();
       }
       tc_fence_before();
