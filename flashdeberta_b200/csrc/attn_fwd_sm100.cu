@@ -470,17 +470,38 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           const int b = 2 * g + ch;
           const uint32_t c0 = b == 3 ? 224u : 64u * uint32_t(b);
           const uint32_t c1 = b == 0 ? 192u : 64u * uint32_t(b) - 32u;
-          uint32_t t0[32], t1[32];
-          if (ok) {
-            tmem_ld32(tmem_lane + kColR + c0, t0);
-            tmem_ld32(tmem_lane + kColR + c1, t1);
-            tmem_wait_ld();
-          }
+          if constexpr (F8) {
+            // the products 16 columns at a time: the e4m3 build has more live values, and three 32-register runs at once
+            // pushed it into spilling
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const uint32_t x = (lane + c <= 30) ? t1[c] : t0[c];
-            const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - c) & 31);
-            s[32 * ch + c] = fmaf(__uint_as_float(y), ratio_p, __uint_as_float(a[c]));
+            for (int hf = 0; hf < 2; ++hf) {
+              uint32_t t0[16], t1[16];
+              if (ok) {
+                tmem_ld16(tmem_lane + kColR + c0 + 16 * hf, t0);
+                tmem_ld16(tmem_lane + kColR + c1 + 16 * hf, t1);
+                tmem_wait_ld();  // the first wait also covers the 32 scores
+              }
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                const int cc = 16 * hf + c;
+                const uint32_t x = (lane + cc <= 30) ? t1[c] : t0[c];
+                const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - cc) & 31);
+                s[32 * ch + cc] = fmaf(__uint_as_float(y), ratio_p, __uint_as_float(a[cc]));
+              }
+            }
+          } else {
+            uint32_t t0[32], t1[32];
+            if (ok) {
+              tmem_ld32(tmem_lane + kColR + c0, t0);
+              tmem_ld32(tmem_lane + kColR + c1, t1);
+              tmem_wait_ld();
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const uint32_t x = (lane + c <= 30) ? t1[c] : t0[c];
+              const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - c) & 31);
+              s[32 * ch + c] = fmaf(__uint_as_float(y), ratio_p, __uint_as_float(a[c]));
+            }
           }
         } else if (F8 && has_p2c && (kind == kSatHi || kind == kSatLo)) {
           // e4m3: the saturated p2c term of these keys sits in the product area (same value in every row)
