@@ -72,9 +72,13 @@ constexpr uint32_t kSmemK = 16384;                  // 2 stages
 constexpr uint32_t kSmemV = 49152;                  // 2 stages
 constexpr uint32_t kSmemWinK = 81920;               // 256 x 128 B window of expanded pos_key
 constexpr uint32_t kSmemWinQ = 114688;              // 256 x 128 B window of expanded pos_query
-constexpr uint32_t kStageCPitch = 272;              // c2p stage [256 positions][128 query rows] bf16, rows padded by 16 B
+// c2p stage: bf16 [128 query rows][256 window positions], rows padded by 16 B.  Row m is rotated by m: position p of the
+// window sits in column (p - m) & 255, so the 64 values a softmax thread needs are one aligned 128-byte run whose place does
+// not depend on m.
+constexpr uint32_t kStageCPitch = 528;
 constexpr uint32_t kSmemStageC = 147456;
-constexpr uint32_t kSmemSat = kSmemStageC + 256 * kStageCPitch;  // 217088: 2 x (8 x 128 B) saturated pos_query rows (hi, lo)
+constexpr uint32_t kSmemSat = kSmemStageC + 69632;  // 217088: 2 x (8 x 128 B) saturated pos_query rows (hi, lo)
+static_assert(128 * kStageCPitch <= 69632, "c2p stage");
 constexpr uint32_t kSmemXchg = kSmemSat + 2048;     // float [2 parities][2 groups][128 rows] row maxima
 constexpr uint32_t kSmemLsum = kSmemXchg + 2048;    // float [2 groups][128 rows] row sums at the end
 constexpr uint32_t kSmemBars = kSmemLsum + 1024;
@@ -197,15 +201,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       if (band_idx > 0) wait(bar(kBarGather), (band_idx - 1u) & 1u);   // nobody reads the previous stage any more
       tc_fence_after();
       if (has_c2p && ok) {
-        // The windows of consecutive band tiles overlap by half: only the first tile of the run brings 256 positions,
-        // every later one the 128 new ones (block 0), written over the half of the stage the new window no longer
-        // covers.  Position p of the current window sits in stage row p ^ flip.
+        // The product has query rows in the lanes and window positions in the columns, so this thread holds row r.  The
+        // windows of consecutive band tiles overlap by half: only the first tile of the run brings 256 positions, every
+        // later one the 128 new ones (block 0), written over the half of the stage the new window no longer covers:
+        // position p of the current window is "physical" position p ^ flip, stored in column (physical - r) & 255.
         const int nblk = band_idx == 0 ? 2 : 1;
         const uint32_t flip = (band_idx & 1u) ? 128u : 0u;
+        const uint32_t row_addr = smem + kSmemStageC + uint32_t(r) * kStageCPitch;
 #pragma unroll 1
         for (int blk = 0; blk < nblk; ++blk) {
-          const uint32_t row_addr = smem + kSmemStageC + (uint32_t(blk * 128 + r) ^ flip) * kStageCPitch;
           const uint32_t col = tmem_lane + kColR + blk * 128;
+          const uint32_t start = ((uint32_t(blk) * 128u) ^ flip) - uint32_t(r);  // column of the block's first position (mod 256)
+          // an odd start puts value 2k-1 and 2k into one 32-bit word: funnel shift over consecutive pairs by 16 bits;
+          // an even start keeps the pairs (shift "32" = take the upper word)
+          const uint32_t sh = (start & 1u) ? 16u : 32u;
+          uint32_t prev = 0;
           uint32_t t[32];
           tmem_ld32(col, t);
           tmem_wait_ld();
@@ -216,10 +226,20 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(__uint_as_float(t[2 * i]), __uint_as_float(t[2 * i + 1]));
             if (c4 < 3) tmem_ld32(col + (c4 + 1) * 32, t);  // the next 32 columns are in flight while these are stored
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-              sts_v4(row_addr + (c4 * 4 + q4) * 16, pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+            for (int k = 0; k < 16; ++k) {
+              const uint32_t word = ((start + uint32_t(32 * c4 + 2 * k)) >> 1) & 127u;
+              const uint32_t v = __funnelshift_rc(k == 0 ? prev : pk[k - 1], pk[k], sh);
+              if (c4 == 0 && k == 0 && (start & 1u)) {
+                // the low half of this word belongs to the other block's last position: write the upper half only
+                sts_u16(row_addr + 4u * word + 2u, pk[0] & 0xffffu);
+              } else {
+                sts_u32(row_addr + 4u * word, v);
+              }
+            }
+            prev = pk[15];
             if (c4 < 3) tmem_wait_ld();
           }
+          if (start & 1u) sts_u16(row_addr + 4u * (((start + 128u) >> 1) & 127u), prev >> 16);  // the block's last value
         }
       }
       tc_fence_before();
@@ -302,15 +322,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             wait(bar(kBarWin), uint32_t(band_idx) & 1u);
             tc_fence_after();
             if (ok && has_c2p) {
-              // c2pT[p][m] = X_k[p].Q[m] in 128-position blocks -> R columns [0,128) (and [128,256) on the first tile of
+              // c2p[m][p] = Q[m].X_k[p] in 128-position blocks -> R columns [0,128) (and [128,256) on the first tile of
               // the run; later tiles reuse the lower half of the previous window from the stage)
               const int nblk = band_idx == 0 ? 2 : 1;
 #pragma unroll 1
               for (int blk = 0; blk < nblk; ++blk)
 #pragma unroll
                 for (int ks = 0; ks < G::kSteps; ++ks)
-                  G::mma(tmem_base + kColR + blk * 128, dwk + uint64_t((blk * G::kTile + ks * 32) >> 4),
-                         dq + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
+                  G::mma(tmem_base + kColR + blk * 128, dq + uint64_t((ks * 32) >> 4),
+                         dwk + uint64_t((blk * G::kTile + ks * 32) >> 4), idesc_s, ks > 0);
             }
             mma_commit(bar(kBarC2p));
             if (ok) {  // the scores do not need R: they are computed while the drain group empties it
@@ -526,15 +546,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
       if (kind == kBand) {
         wait(bar(kBarStage), band_idx & 1u);  // the c2p stage of this tile is complete
         if (has_c2p) {
-          // c2p[m][i] is position p = m + 127 - i of the window, query column m; position p sits in stage row p ^ flip
-          // (see the drain group): 128 rows up for the new half (p < 128 <=> i >= m), 128 rows down for the kept one
-          const uint32_t base = smem + kSmemStageC + uint32_t(r + 127 - 64 * g) * kStageCPitch + uint32_t(r) * 2u;
-          const uint32_t fl = (band_idx & 1u) ? 128u * kStageCPitch : 0u;
-          const uint32_t base_new = base + fl, base_old = base - fl;
-          const int thr = r - 64 * g;
+          // c2p[m][i] is position p = m + 127 - i of the window, stored in column ((p ^ flip) - m) & 255 of row m (see the
+          // drain group): for this thread's keys i = 64g .. 64g+63 that is the aligned run of 64 columns ending at
+          // 127 - 64g (+ 128 when flipped), read with eight 16-byte loads, key i in column (run start) + 63 - (i - 64g).
+          const uint32_t run = smem + kSmemStageC + uint32_t(r) * kStageCPitch +
+                               2u * (uint32_t(64 * (1 - g)) + ((band_idx & 1u) ? 128u : 0u));
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            s[i] = fmaf(bf16_bits_to_f32(lds_u16((i >= thr ? base_new : base_old) - uint32_t(i) * kStageCPitch)), ratio_c, s[i]);
+          for (int q = 0; q < 8; ++q) {
+            const uint4 w4 = lds_v4(run + 16u * uint32_t(q));
+            const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {  // column 8q + e of the run -> key 63 - (8q + e)
+              const uint32_t bits = (e & 1) ? (w[e >> 1] & 0xffff0000u) : (w[e >> 1] << 16);
+              s[63 - (8 * q + e)] = fmaf(__uint_as_float(bits), ratio_c, s[63 - (8 * q + e)]);
+            }
+          }
         }
         mbar_arrive(bar(kBarGather));
         ++band_idx;
