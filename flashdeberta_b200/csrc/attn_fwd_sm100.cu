@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         const uint32_t row_addr = smem + kSmemStageC + uint32_t(r) * kStageCPitch;
 #pragma unroll 1
         for (int blk = 0; blk < nblk; ++blk) {
-          const uint32_t col = tmem_lane + kColR + blk * 128;
+          const uint32_t col = tmem_lane + (band_idx == 0 ? kColR + blk * 128 : kColS);  // see the score-issuing warp
           const uint32_t start = ((uint32_t(blk) * 128u) ^ flip) - uint32_t(r);  // column of the block's first position (mod 256)
           // an odd start puts value 2k-1 and 2k into one 32-bit word: funnel shift over consecutive pairs by 16 bits;
           // an even start keeps the pairs (shift "32" = take the upper word)
@@ -321,25 +321,32 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           if (kind == kBand) {
             wait(bar(kBarWin), uint32_t(band_idx) & 1u);
             tc_fence_after();
+            // Order of issue.  First band tile of the run: c2p (two 128-position blocks) -> R, scores -> S, and once the
+            // drain group has emptied R, the p2c products -> R.  Later tiles bring one c2p block, and it goes to the S
+            // columns (free until this tile's scores are computed), so the p2c products can be issued into R at once and
+            // run while the drain group works; only the four score MMAs wait for the drain.
+            const bool first = band_idx == 0;
             if (ok && has_c2p) {
-              // c2p[m][p] = Q[m].X_k[p] in 128-position blocks -> R columns [0,128) (and [128,256) on the first tile of
-              // the run; later tiles reuse the lower half of the previous window from the stage)
-              const int nblk = band_idx == 0 ? 2 : 1;
+              // c2p[m][p] = Q[m].X_k[p] in 128-position blocks (later tiles reuse the lower half of the previous window
+              // from the stage)
+              const int nblk = first ? 2 : 1;
 #pragma unroll 1
               for (int blk = 0; blk < nblk; ++blk)
 #pragma unroll
                 for (int ks = 0; ks < G::kSteps; ++ks)
-                  G::mma(tmem_base + kColR + blk * 128, dq + uint64_t((ks * 32) >> 4),
+                  G::mma(tmem_base + (first ? kColR + blk * 128 : kColS), dq + uint64_t((ks * 32) >> 4),
                          dwk + uint64_t((blk * G::kTile + ks * 32) >> 4), idesc_s, ks > 0);
             }
             mma_commit(bar(kBarC2p));
-            if (ok) {  // the scores do not need R: they are computed while the drain group empties it
+            if (ok && first) {
 #pragma unroll
               for (int ks = 0; ks < G::kSteps; ++ks)
                 G::mma(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             }
-            wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
-            tc_fence_after();
+            if (first) {
+              wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
+              tc_fence_after();
+            }
             if (ok && has_p2c) {
               // p2c products.  Key block b (32 keys) needs X_q rows starting at 32(3-b) (t = 0) and 32(4-b) (t = 1); blocks
               // b and b+1 share the start row 32(3-b), so three 128x64 products cover six of the eight (b, t) pairs and
@@ -364,6 +371,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
               for (int ks = 0; ks < G::kSteps; ++ks)
                 G::mma(tmem_base + kColR + 224, dwq + uint64_t((ks * 32) >> 4),
                        dk + 3 * blk32 + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
+            }
+            if (!first) {
+              wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of S
+              tc_fence_after();
+              if (ok) {
+#pragma unroll
+                for (int ks = 0; ks < G::kSteps; ++ks)
+                  G::mma(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
+              }
             }
             ++band_idx;
           } else {
