@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
           uint32_t t[32];
           tmem_ld32(col, t);
           tmem_wait_ld();
-#pragma unroll
+#pragma unroll 1  // kept rolled: this loop runs beside the softmax warps, whose unrolled code already fills the instruction cache
           for (int c4 = 0; c4 < 4; ++c4) {
             uint32_t pk[16];
 #pragma unroll
