@@ -32,10 +32,13 @@ from transformers.models.deberta_v2.modeling_deberta_v2 import (
     DebertaV2ForTokenClassification,
     DebertaV2Layer,
     DebertaV2Model,
+    DebertaV2Output,
+    DebertaV2SelfOutput,
     DebertaV2PreTrainedModel,
     DisentangledSelfAttention,
 )
 
+from . import ops
 from .attention import FlashDisentangledSelfAttention, PackedSequences, lengths_from_mask
 
 __all__ = [
@@ -60,16 +63,46 @@ def _backend(config) -> str:
     return name
 
 
+def _dense_add_layernorm(block, hidden_states, input_tensor):
+    """dense -> dropout -> LayerNorm(hidden + input) of transformers' DebertaV2SelfOutput / DebertaV2Output, with the add
+    and the normalisation in one kernel when the case allows it (inference, CUDA, bf16)."""
+    hidden_states = block.dense(hidden_states)
+    ln = block.LayerNorm
+    if (not block.training and ln.elementwise_affine
+            and ops.can_fuse_add_layernorm(hidden_states, ln.weight, ln.bias) and input_tensor.dtype == hidden_states.dtype
+            and not torch.is_grad_enabled()):
+        return ops.add_layernorm(hidden_states, input_tensor, ln.weight, ln.bias, ln.eps)
+    return ln(block.dropout(hidden_states) + input_tensor)
+
+
+class FlashDebertaV2SelfOutput(DebertaV2SelfOutput):
+    """Same parameters as transformers' block (the reference keeps it, src/flashdeberta/model.py:259-262)."""
+
+    def forward(self, hidden_states, input_tensor):
+        return _dense_add_layernorm(self, hidden_states, input_tensor)
+
+
+class FlashDebertaV2Output(DebertaV2Output):
+    """Same parameters as transformers' block (src/flashdeberta/model.py:265-272)."""
+
+    def forward(self, hidden_states, input_tensor):
+        return _dense_add_layernorm(self, hidden_states, input_tensor)
+
+
 class FlashDebertaV2Attention(DebertaV2Attention):
     def __init__(self, config):
         super().__init__(config)
         self.self = DEBERTA_SELF_ATTENTION_CLASSES[_backend(config)](config)
+        if _backend(config) != "eager":
+            self.output = FlashDebertaV2SelfOutput(config)
 
 
 class FlashDebertaV2Layer(DebertaV2Layer):
     def __init__(self, config):
         super().__init__(config)
         self.attention = FlashDebertaV2Attention(config)
+        if _backend(config) != "eager":
+            self.output = FlashDebertaV2Output(config)
 
 
 class FlashDebertaV2Encoder(DebertaV2Encoder):

@@ -18,7 +18,7 @@ import torch
 from . import _lib, bucket
 
 __all__ = [
-    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3",
+    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3", "add_layernorm", "can_fuse_add_layernorm",
     "check_status", "launch_count",
 ]
 
@@ -323,6 +323,42 @@ def quantize_e4m3(x: torch.Tensor, slab_start: torch.Tensor) -> Tuple[torch.Tens
                                          scale.data_ptr(), C.c_void_p(stream)))
         _launches += 1
     return y.view(x.shape), scale
+
+
+def can_fuse_add_layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
+    """True when ``add_layernorm`` covers this case: CUDA bf16 activations and parameters, hidden a multiple of 256 up to
+    2048."""
+    hidden = x.shape[-1]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and bias is not None and weight.dtype == torch.bfloat16
+            and bias.dtype == torch.bfloat16 and hidden % 256 == 0 and hidden <= 2048)
+
+
+def add_layernorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
+                  eps: float) -> torch.Tensor:
+    """LayerNorm(x + residual) over the last dimension in one pass (``fdb_add_layernorm``): the tail of transformers'
+    DebertaV2SelfOutput / DebertaV2Output, which the reference's layer classes keep (src/flashdeberta/model.py:259-272).
+    bf16 in and out, fp32 statistics, the sum rounded to bf16 first as in the eager expression."""
+    global _launches
+    if not can_fuse_add_layernorm(x, weight, bias):
+        raise ValueError("add_layernorm needs CUDA bf16 tensors with hidden a multiple of 256 up to 2048")
+    lib = _lib.load()
+    hidden = x.shape[-1]
+    x2 = x.reshape(-1, hidden)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    r2 = None
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype or residual.device != x.device:
+            raise ValueError("residual must match x in shape, dtype and device")
+        r2 = residual.reshape(-1, hidden)
+        r2 = r2 if r2.is_contiguous() else r2.contiguous()
+    out = torch.empty_like(x2)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(lib.fdb_add_layernorm(x2.data_ptr(), r2.data_ptr() if r2 is not None else None,
+                                         weight.contiguous().data_ptr(), bias.contiguous().data_ptr(), out.data_ptr(),
+                                         x2.shape[0], hidden, float(eps), C.c_void_p(stream)))
+        _launches += 1
+    return out.view(x.shape)
 
 
 # --------------------------------------------------------------------------------------------------------------------

@@ -202,6 +202,17 @@ FDB_API int fdb_relative_index_matrix(const int16_t* bucket_lut, int32_t lut_d_m
 FDB_API int fdb_quantize_e4m3(const void* x_bf16, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
                       int32_t n_slabs, int32_t heads, int32_t head_dim, void* y_e4m3, float* scale, void* stream);
 
+/*
+ * out = LayerNorm(x + residual) over the last dimension (eps inside the square root), bf16 in and out, fp32 statistics; the
+ * sum is rounded to bf16 first, as the eager expression does.  Replaces the tail of both output blocks of a layer, which
+ * the reference inherits from transformers: DebertaV2SelfOutput / DebertaV2Output `LayerNorm(dropout(dense(h)) + input)`
+ * behind FlashDebertaV2Attention / FlashDebertaV2Layer (src/flashdeberta/model.py:259-272) — there an elementwise add
+ * and a layer-norm kernel, here one pass.  x, residual (may be NULL: plain LayerNorm), out: (rows, hidden) contiguous;
+ * gamma, beta: (hidden) bf16; hidden a multiple of 256 up to 2048; every pointer 16-byte aligned.
+ */
+FDB_API int fdb_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
+                              int64_t rows, int32_t hidden, float eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -528,6 +528,42 @@ def test_sharded_ragged_batch_matches_whole_batch():
     assert d.max().item() < 0.1 and d.mean().item() < 5e-3, (d.max().item(), d.mean().item())
 
 
+@pytest.mark.parametrize("rows,hidden,with_residual", [(1000, 768, True), (37, 1024, True), (5, 256, False),
+                                                       (16384, 768, True), (129, 2048, True), (1, 1536, True)])
+def test_add_layernorm_vs_fp32_and_torch(rows, hidden, with_residual):
+    """fdb_add_layernorm against an fp32 restatement of LayerNorm(bf16(x + r)) (bf16 output rounding: one ulp) and against
+    torch's own bf16 add + layer_norm."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(rows + hidden)
+    x = (torch.randn(rows, hidden, generator=g) * 2).bfloat16()
+    r = torch.randn(rows, hidden, generator=g).bfloat16() if with_residual else None
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16()
+    b = (0.1 * torch.randn(hidden, generator=g)).bfloat16()
+    eps = 1e-7
+    out = ops.add_layernorm(x.to(DEV), r.to(DEV) if with_residual else None, w.to(DEV), b.to(DEV), eps)
+    torch.cuda.synchronize()
+    s = (x + r).float() if with_residual else x.float()  # bf16 sum, as the eager expression
+    want = torch.nn.functional.layer_norm(s, (hidden,), w.float(), b.float(), eps)
+    err = (out.float().cpu() - want).abs()
+    assert err.max().item() <= 4e-2 and err.mean().item() <= 3e-3, (err.max().item(), err.mean().item())
+    tref = torch.nn.functional.layer_norm((x.to(DEV) + r.to(DEV)) if with_residual else x.to(DEV), (hidden,), w.to(DEV),
+                                          b.to(DEV), eps)
+    # same fp32 statistics, same rounding: at most one bf16 ulp apart, and equal almost everywhere
+    diff = (out.float() - tref.float()).abs()
+    assert diff.max().item() <= 6.3e-2 and (diff > 0).float().mean().item() < 0.1
+
+
+def test_add_layernorm_rejects_what_it_does_not_cover():
+    ops = _ops()
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.ones(100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        ops.add_layernorm(x, None, w, w, 1e-7)
+    x32 = torch.zeros(4, 256, dtype=torch.float32, device=DEV)
+    with pytest.raises(ValueError):
+        ops.add_layernorm(x32, None, w, w, 1e-7)
+
+
 def test_unsupported_inputs_raise():
     from flashdeberta_b200 import _lib
     ops = _ops()
