@@ -106,16 +106,57 @@ __global__ void __launch_bounds__(kScanThreads) seq_info_kernel(const int32_t* _
     partial[t] += add;
     __syncthreads();
   }
+  const int32_t total_tiles = partial[kScanThreads - 1];
   int32_t run = partial[t] - sum;  // exclusive
   for (int b = b0; b < b1; ++b) {
     tile_first[b] = run;
-    const int start = seq_info[2 * b], len = seq_info[2 * b + 1];
-    const int tiles = packed ? (len + kTileM - 1) / kTileM : dense_tiles;
-    for (int i = 0; i < tiles && run + i < slots; ++i) slot_info[run + i] = make_int4(b, i * kTileM, start, len);
-    run += tiles;
+    run += packed ? (seq_info[2 * b + 1] + kTileM - 1) / kTileM : dense_tiles;
   }
-  if (t == kScanThreads - 1) tile_first[batch] = partial[t];
-  for (int i = partial[kScanThreads - 1] + t; i < slots; i += kScanThreads) slot_info[i] = make_int4(-1, 0, 0, 0);
+  if (t == kScanThreads - 1) tile_first[batch] = total_tiles;
+  __syncthreads();
+
+  // Slot table: the order in which the fused kernels' CTAs take the query tiles.  A query tile costs in proportion to its
+  // sequence's length, so the sequences go longest first (ties by index): the last CTAs of a ragged batch are then the
+  // cheap ones.  With more sequences than threads the order stays that of the batch.
+  if (batch <= kScanThreads) {
+    __shared__ int32_t tiles_by_rank[kScanThreads];
+    int len = 0, start = 0, tiles = 0, rank = 0;
+    if (t < batch) {
+      start = seq_info[2 * t];
+      len = seq_info[2 * t + 1];
+      tiles = packed ? (len + kTileM - 1) / kTileM : dense_tiles;
+      for (int o = 0; o < batch; ++o) {
+        const int lo = seq_info[2 * o + 1];
+        rank += (lo > len || (lo == len && o < t)) ? 1 : 0;
+      }
+    }
+    __syncthreads();                 // `partial` is free again
+    partial[t] = 0;
+    __syncthreads();
+    if (t < batch) tiles_by_rank[rank] = tiles;
+    __syncthreads();
+    partial[t] = t < batch ? tiles_by_rank[t] : 0;
+    __syncthreads();
+    for (int o = 1; o < kScanThreads; o <<= 1) {
+      const int32_t add = t >= o ? partial[t - o] : 0;
+      __syncthreads();
+      partial[t] += add;
+      __syncthreads();
+    }
+    if (t < batch) {
+      const int32_t first = partial[rank] - tiles;  // exclusive prefix in rank order
+      for (int i = 0; i < tiles && first + i < slots; ++i) slot_info[first + i] = make_int4(t, i * kTileM, start, len);
+    }
+  } else {
+    int32_t at = partial[t] - sum;
+    for (int b = b0; b < b1; ++b) {
+      const int start = seq_info[2 * b], len = seq_info[2 * b + 1];
+      const int tiles = packed ? (len + kTileM - 1) / kTileM : dense_tiles;
+      for (int i = 0; i < tiles && at + i < slots; ++i) slot_info[at + i] = make_int4(b, i * kTileM, start, len);
+      at += tiles;
+    }
+  }
+  for (int i = total_tiles + t; i < slots; i += kScanThreads) slot_info[i] = make_int4(-1, 0, 0, 0);
   if (bad && status != nullptr) atomicOr(reinterpret_cast<unsigned int*>(status), FDB_DEV_BAD_SEQLEN);
 }
 
