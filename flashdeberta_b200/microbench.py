@@ -5,6 +5,10 @@ their operands in L2).
 
 Prints one JSON line: median/min ms per launch and algorithmic TFLOP/s (4*l^2*D + 2*l*2S*D per position term, per
 sequence and head).
+
+    python -m flashdeberta_b200.microbench --add-layernorm --rows 16384 --hidden 768
+
+times the fused residual + LayerNorm kernel instead (algorithmic bytes: 3 * rows * hidden * 2, four rotated buffers).
 """
 from __future__ import annotations
 
@@ -21,6 +25,30 @@ def attn_flops(lengths, heads, head_dim=64, span=256, c2p=True, p2c=True):
     return sum(heads * (4 * n * n * head_dim + (int(c2p) + int(p2c)) * 2 * n * 2 * span * head_dim) for n in lengths)
 
 
+def bench_add_layernorm(rows: int, hidden: int, iters: int, warmup: int, sets: int):
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(0)
+    xs = [torch.randn(rows, hidden, generator=g).bfloat16().to(dev) for _ in range(sets)]
+    rs = [torch.randn(rows, hidden, generator=g).bfloat16().to(dev) for _ in range(sets)]
+    w, b = torch.ones(hidden, dtype=torch.bfloat16, device=dev), torch.zeros(hidden, dtype=torch.bfloat16, device=dev)
+    for i in range(warmup):
+        ops.add_layernorm(xs[i % sets], rs[i % sets], w, b, 1e-7)
+    torch.cuda.synchronize()
+    times = []
+    for i in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.add_layernorm(xs[i % sets], rs[i % sets], w, b, 1e-7)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    nbytes = 3 * rows * hidden * 2
+    med, mn = statistics.median(times), min(times)
+    print(json.dumps({"op": "add_layernorm", "rows": rows, "hidden": hidden, "ms_median": med, "ms_min": mn,
+                      "gbs_median": nbytes / med / 1e6, "gbs_best": nbytes / mn / 1e6, "bytes": nbytes,
+                      "l2": f"{sets} buffer sets rotated ({sets * 3 * rows * hidden * 2 >> 20} MiB; the output is allocated per call)"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=8)
@@ -32,7 +60,12 @@ def main():
     ap.add_argument("--no-pos", action="store_true")
     ap.add_argument("--fp8", action="store_true", help="e4m3 operands (quantised once, outside the timed region)")
     ap.add_argument("--valid", type=int, default=0, help="valid length of every sequence (default: all)")
+    ap.add_argument("--add-layernorm", action="store_true", help="time fdb_add_layernorm instead of the attention")
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--hidden", type=int, default=768)
     args = ap.parse_args()
+    if args.add_layernorm:
+        return bench_add_layernorm(args.rows, args.hidden, args.iters, args.warmup, max(args.sets, 8))
     dev = torch.device("cuda")
     B, L, H, D = args.batch, args.seq, args.heads, 64
     g = torch.Generator(device="cpu").manual_seed(0)
