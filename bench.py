@@ -370,6 +370,87 @@ def varlen_run(args):
         dist.destroy_process_group()
 
 
+def fp8_run(args):
+    """Extra measurement (not the headline line): the e4m3 configuration — DeBERTa-v3-large encoder, random-init, attention
+    operands quantised to e4m3 with per-(sequence, head) scales (`config.attn_fp8`), linears in bf16; 8 sequences of 4096
+    tokens per GPU (the per-GPU share of the 64-sequence batch at 8 GPUs; weak scaling), ids uniform from seed 4.  Also times
+    the bf16 attention on the same model and inputs.  Prints one JSON line with "config": {"workload": "fp8 ..."}."""
+    import torch.distributed as dist
+    from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+    from flashdeberta_b200 import ops
+    from flashdeberta_b200.model import FlashDebertaV2Model
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, L = 8, 4096
+
+    def build(fp8: bool):
+        cfg = DebertaV2Config(
+            vocab_size=128100, hidden_size=1024, num_hidden_layers=24, num_attention_heads=16, intermediate_size=4096,
+            hidden_act="gelu", max_position_embeddings=512, type_vocab_size=0, layer_norm_eps=1e-7,
+            relative_attention=True, max_relative_positions=-1, position_buckets=256, norm_rel_ebd="layer_norm",
+            share_att_key=True, pos_att_type="c2p|p2c", position_biased_input=False, pad_token_id=0)
+        cfg.attn_backend = "b200"
+        cfg.attn_fp8 = fp8
+        torch.manual_seed(4)
+        return FlashDebertaV2Model(cfg).eval().to(dev).to(torch.bfloat16)
+
+    g = torch.Generator(device="cpu").manual_seed(4 + rank)
+    ids = torch.randint(1, 128100, (B, L), generator=g).to(dev)
+    mask = torch.ones(B, L, dtype=torch.long, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(model):
+        with torch.no_grad():
+            for _ in range(max(args.warmup, 3)):
+                model(input_ids=ids, attention_mask=mask)
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(args.steps):
+                out = model(input_ids=ids, attention_mask=mask).last_hidden_state
+            t1.record()
+            barrier()
+            ms = t0.elapsed_time(t1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = t.item()
+            ops.check_status(dev)
+        return ms / args.steps, out
+
+    m8 = build(True)
+    ms8, out8 = timed(m8)
+    del m8
+    m16 = build(False)
+    ms16, out16 = timed(m16)
+    diff = (out8.float() - out16.float()).abs()
+    if rank == 0:
+        tokens = B * L * world
+        f = 24 * attn_flops([L] * B, heads=16) + encoder_linear_flops(B * L, 1024, 4096, 24)
+        print(json.dumps({
+            "metric": "deberta_v3_large_encoder_tokens_per_s", "value": tokens / (ms8 / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "ms_per_step": ms8, "scaling": "weak", "dtype": "e4m3 attention, bf16 linears",
+            "data": "synthetic",
+            "config": {"workload": "fp8: DeBERTa-v3-large encoder, 8 x 4096 tokens per GPU, e4m3 attention operands with "
+                                   "per-(sequence, head) scales (seed 4)", "global_batch": B * world, "seq_len": L,
+                       "parallelism": f"dp{world}"},
+            "bf16_attention_ms_per_step": ms16, "bf16_attention_tokens_per_s": tokens / (ms16 / 1e3),
+            "last_hidden_state_vs_bf16_attention": {"max_abs": diff.max().item(), "mean_abs": diff.mean().item()},
+            "model_tflops": f / (ms8 / 1e3) / 1e12}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,9 +459,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--varlen", action="store_true", help="measure the packed v3-large configuration instead")
+    ap.add_argument("--fp8", action="store_true", help="measure the e4m3-attention v3-large configuration instead")
     args = ap.parse_args()
     if args.varlen:
         varlen_run(args)
+    elif args.fp8:
+        fp8_run(args)
     elif args.impl == "reference":
         reference_arm(args)
     else:

@@ -136,3 +136,42 @@ def test_ops_refuse_cpu_tensors():
     x = torch.zeros(1, 8, 1, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         ops.disentangled_attention(x, x, x, None, None, max_seqlen=8)
+
+
+@pytest.mark.parametrize("x,gamma,hidden,code", [
+    (0, 0x1000, 768, -1),          # x NULL
+    (0x1000, 0, 768, -1),          # gamma NULL
+    (0x1000, 0x1000, 100, -2),     # hidden not a multiple of 256
+    (0x1000, 0x1000, 4096, -2),    # hidden above 2048
+    (0x1008, 0x1000, 768, -3),     # x not 16-byte aligned
+])
+def test_add_layernorm_argument_errors(x, gamma, hidden, code):
+    lib = _lib.load()
+    rc = lib.fdb_add_layernorm(x or None, None, gamma or None, 0x1000, 0x2000, 4, hidden, 1e-7, None)
+    assert rc == code
+    assert lib.fdb_last_error().decode() != ""
+
+
+def test_add_layernorm_zero_rows_is_a_no_op():
+    lib = _lib.load()
+    assert lib.fdb_add_layernorm(0x1000, None, 0x1000, 0x1000, 0x2000, 0, 768, 1e-7, None) == 0
+
+
+def test_layer_output_blocks_keep_transformers_parameter_names():
+    """The blocks that call the fused add + LayerNorm are drop-in for transformers' (same state-dict keys), and fall back to
+    transformers' own expression on CPU tensors."""
+    from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DebertaV2Layer
+    from flashdeberta_b200.model import FlashDebertaV2Layer
+    cfg = DebertaV2Config(hidden_size=256, num_attention_heads=4, intermediate_size=512, num_hidden_layers=1,
+                          relative_attention=True, position_buckets=32, max_relative_positions=64,
+                          pos_att_type="c2p|p2c", share_att_key=True, vocab_size=100, type_vocab_size=0)
+    cfg.attn_backend = "b200"
+    torch.manual_seed(0)
+    ours, theirs = FlashDebertaV2Layer(cfg).eval(), DebertaV2Layer(cfg).eval()
+    assert set(ours.state_dict().keys()) == set(theirs.state_dict().keys())
+    theirs.load_state_dict(ours.state_dict())
+    h, x = torch.randn(2, 5, 512), torch.randn(2, 5, 256)
+    with torch.no_grad():
+        assert torch.equal(ours.output(h, x), theirs.output(h, x))
+        assert torch.equal(ours.attention.output(x, x), theirs.attention.output(x, x))
