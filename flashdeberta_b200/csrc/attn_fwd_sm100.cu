@@ -783,7 +783,13 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   // follow in attn_fwd_kernel, which picks up the partial result on the same stream.
   const bool no_pos = a.xk == nullptr && a.xq == nullptr;
   if (!f8 && (w.split || (no_pos && use_far_for_plain()))) {
-    if ((rc = launch_attn_fwd_far(&a, slots, p.heads, stream)) != FDB_OK) return rc;
+    // Two forms of the far kernel: one team per CTA and two CTAs per SM (the start and the end of a CTA overlap the other
+    // CTA's work: better up to about 8192 keys), or two teams in one CTA with three K/V stages (better beyond).
+    // FDB_ATTN_FAR=1|2 forces one of them.
+    const char* far = std::getenv("FDB_ATTN_FAR");
+    const bool one_team = far != nullptr && (far[0] == '1' || far[0] == '2') ? far[0] == '1' : p.max_seqlen <= 8192;
+    rc = one_team ? launch_attn_fwd_far1(&a, slots, p.heads, stream) : launch_attn_fwd_far(&a, slots, p.heads, stream);
+    if (rc != FDB_OK) return rc;
     if (no_pos) return FDB_OK;
   }
 

@@ -263,7 +263,8 @@ def test_fused_position_variants(c2p, p2c, buckets, max_rel):
 
 @pytest.mark.parametrize("c2p,p2c", [(True, True), (True, False), (False, True)])
 @pytest.mark.parametrize("packed", [False, True])
-def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c, packed):
+@pytest.mark.parametrize("far", ["1", "2"])
+def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c, packed, far):
     """Sequences long enough to have saturated key tiles on both sides of the band, run with the far key tiles in the
     two-team kernel and the band tiles in a second launch (forced through FDB_ATTN_SPLIT, which the library reads on
     every call; long calls take this path by themselves), against the single launch and the CPU oracle."""
@@ -286,6 +287,7 @@ def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c,
     to = lambda t: None if t is None else t.to(DEV)
     args = (to(q), to(k), to(v), to(pk), to(pq))
     kw.update(sm_scale=sm, position_buckets=buckets, max_relative_positions=max_rel, return_lse=True)
+    monkeypatch.setenv("FDB_ATTN_FAR", far)  # the far key tiles by the one-team or the two-team kernel
     monkeypatch.setenv("FDB_ATTN_SPLIT", "1")
     out2, lse2 = ops.disentangled_attention(*args, **kw)
     monkeypatch.setenv("FDB_ATTN_SPLIT", "0")
@@ -303,8 +305,10 @@ def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c,
 
 
 @pytest.mark.parametrize("lens", [[1], [128], [129], [300, 129, 7], [1000, 1000], [2050, 1, 1279]])
-def test_position_free_ragged_lengths(lens):
-    """No position terms at all (plain softmax attention): every key tile goes through the two-team kernel."""
+@pytest.mark.parametrize("far", ["1", "2"])
+def test_position_free_ragged_lengths(monkeypatch, lens, far):
+    """No position terms at all (plain softmax attention): every key tile goes through one of the two far kernels."""
+    monkeypatch.setenv("FDB_ATTN_FAR", far)
     ops = _ops()
     H, D = 2, 64
     q, k, v, _, _ = _random(21 + len(lens), (sum(lens),), H, 1, False, False)
