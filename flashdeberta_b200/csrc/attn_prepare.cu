@@ -35,7 +35,7 @@ static bool want_split(const fdb_attn_params& p) {
   const char* env = std::getenv("FDB_ATTN_SPLIT");
   if (env != nullptr && env[0] == '0') return false;
   if (env != nullptr && env[0] == '1') return true;
-  return p.max_seqlen >= 4096;
+  return p.max_seqlen >= 3584;
 }
 
 int64_t tile_slots(const fdb_attn_params& p) {
