@@ -144,6 +144,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
     return d0 >= args.sat_hi ? kSatHi : (d0 + 254 <= args.sat_lo ? kSatLo : kBand);
   };
 
+  // When the CTA's very first key tile is a band tile, the output and P columns are still unused: the two c2p blocks of
+  // that tile go to the S columns and to O|P instead of R, so its p2c products need not wait for the drain group.
+  const bool c2p_outside_r = !resume && n_proc > 0 && tile_kind(j_first) == kBand;
+
   auto bar = [&](uint32_t i) -> uint32_t { return smem + kSmemBars + 8u * i; };
   const uint32_t tmem_slot = smem + kSmemBars + 8u * kNumBars;
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + kSmemBars + 8u * kNumBars + 8u);
@@ -210,7 +214,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
         const uint32_t row_addr = smem + kSmemStageC + uint32_t(r) * kStageCPitch;
 #pragma unroll 1
         for (int blk = 0; blk < nblk; ++blk) {
-          const uint32_t col = tmem_lane + (band_idx == 0 ? kColR + blk * 128 : kColS);  // see the score-issuing warp
+          // where the score-issuing warp put the block (see there)
+          const uint32_t col = tmem_lane + (band_idx > 0 ? kColS : (c2p_outside_r ? (blk == 0 ? kColS : kColO) : kColR + blk * 128));
           const uint32_t start = ((uint32_t(blk) * 128u) ^ flip) - uint32_t(r);  // column of the block's first position (mod 256)
           // an odd start puts value 2k-1 and 2k into one 32-bit word: funnel shift over consecutive pairs by 16 bits;
           // an even start keeps the pairs (shift "32" = take the upper word)
@@ -324,7 +329,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
             // Order of issue.  First band tile of the run: c2p (two 128-position blocks) -> R, scores -> S, and once the
             // drain group has emptied R, the p2c products -> R.  Later tiles bring one c2p block, and it goes to the S
             // columns (free until this tile's scores are computed), so the p2c products can be issued into R at once and
-            // run while the drain group works; only the four score MMAs wait for the drain.
+            // run while the drain group works; only the four score MMAs wait for the drain.  The same holds for a first
+            // band tile that is the CTA's first tile at all (c2p_outside_r).
             const bool first = band_idx == 0;
             if (ok && has_c2p) {
               // c2p[m][p] = Q[m].X_k[p] in 128-position blocks (later tiles reuse the lower half of the previous window
@@ -334,16 +340,17 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
               for (int blk = 0; blk < nblk; ++blk)
 #pragma unroll
                 for (int ks = 0; ks < G::kSteps; ++ks)
-                  G::mma(tmem_base + (first ? kColR + blk * 128 : kColS), dq + uint64_t((ks * 32) >> 4),
-                         dwk + uint64_t((blk * G::kTile + ks * 32) >> 4), idesc_s, ks > 0);
+                  G::mma(tmem_base + (!first ? kColS : (c2p_outside_r ? (blk == 0 ? kColS : kColO) : kColR + blk * 128)),
+                         dq + uint64_t((ks * 32) >> 4), dwk + uint64_t((blk * G::kTile + ks * 32) >> 4), idesc_s, ks > 0);
             }
             mma_commit(bar(kBarC2p));
-            if (ok && first) {
+            const bool scores_last = !first || c2p_outside_r;  // a c2p block sits in the S columns until it is drained
+            if (ok && !scores_last) {
 #pragma unroll
               for (int ks = 0; ks < G::kSteps; ++ks)
                 G::mma(tmem_base + kColS, dq + uint64_t((ks * 32) >> 4), dk + uint64_t((ks * 32) >> 4), idesc_s, ks > 0);
             }
-            if (first) {
+            if (!scores_last) {
               wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of R
               tc_fence_after();
             }
@@ -372,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
                 G::mma(tmem_base + kColR + 224, dwq + uint64_t((ks * 32) >> 4),
                        dk + 3 * blk32 + uint64_t((ks * 32) >> 4), idesc_p2c, ks > 0);
             }
-            if (!first) {
+            if (scores_last) {
               wait(bar(kBarStage), uint32_t(band_idx) & 1u);  // the drain group has moved the c2p product out of S
               tc_fence_after();
               if (ok) {

@@ -144,8 +144,21 @@ __global__ void __launch_bounds__(kScanThreads) seq_info_kernel(const int32_t* _
       __syncthreads();
     }
     if (t < batch) {
+      // Within a sequence the query tiles away from both ends come first: they have the most band key tiles (the
+      // expensive kind), so the CTAs that run last are the cheaper ones.
       const int32_t first = partial[rank] - tiles;  // exclusive prefix in rank order
-      for (int i = 0; i < tiles && first + i < slots; ++i) slot_info[first + i] = make_int4(t, i * kTileM, start, len);
+      int pos = 0;
+      auto emit = [&](int i) {
+        if (first + pos < slots) slot_info[first + pos] = make_int4(t, i * kTileM, start, len);
+        ++pos;
+      };
+      for (int i = 4; i <= tiles - 5; ++i) emit(i);
+      for (int k = 3; k >= 0; --k) {
+        const int lo = k, hi = tiles - 1 - k;
+        if (lo > hi) continue;
+        emit(lo);
+        if (hi != lo) emit(hi);
+      }
     }
   } else {
     int32_t at = partial[t] - sum;
