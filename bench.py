@@ -125,6 +125,13 @@ def cpu_eager_run(steps: int, warmup: int, budget_s: float):
     """Full 12-layer encoder on ONE sequence of SEQ_LEN tokens per step (the eager path holds a B*H*L^2 fp32 score tensor,
     so the 8-sequence batch is sampled by one of its sequences).  Returns (tokens/s, ms/step, steps timed, threads)."""
     from flashdeberta_b200.model import FlashDebertaV2Model
+    # every host core this process may run on (torchrun sets OMP_NUM_THREADS=1 for its children, which would leave the
+    # baseline single-threaded)
+    try:
+        usable = len(os.sched_getaffinity(0))
+    except AttributeError:
+        usable = os.cpu_count() or 1
+    torch.set_num_threads(max(1, usable))
     threads = torch.get_num_threads()
     torch.manual_seed(1)
     model = FlashDebertaV2Model(v3_base_config("eager")).eval()
