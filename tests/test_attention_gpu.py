@@ -568,6 +568,31 @@ def test_add_layernorm_rejects_what_it_does_not_cover():
         ops.add_layernorm(x32, None, w, w, 1e-7)
 
 
+def test_call_can_be_captured_in_a_cuda_graph_and_replayed():
+    """No host synchronisation, no allocation inside the library: a call (set-up kernels + fused kernel) is capturable;
+    the replay on new inputs matches a direct call bit for bit."""
+    ops = _ops()
+    H, D, B, L = 4, 64, 2, 700
+    lens = torch.tensor([700, 333], dtype=torch.int32, device=DEV)
+    kw = dict(max_seqlen=L, position_buckets=256, max_relative_positions=512, seq_lens=lens)
+    qa, ka, va, pk, pq = (t.to(DEV) for t in _random(31, (B, L), H, 256))
+    qb, kb, vb, _, _ = (None if t is None else t.to(DEV) for t in _random(32, (B, L), H, 256))
+    sq, sk, sv = qa.clone(), ka.clone(), va.clone()      # static inputs of the graph
+    ops.disentangled_attention(sq, sk, sv, pk, pq, **kw)  # warm-up outside capture (library handles, allocator pools)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_static = ops.disentangled_attention(sq, sk, sv, pk, pq, **kw)
+    for q, k, v in ((qb, kb, vb), (qa, ka, va)):
+        sq.copy_(q); sk.copy_(k); sv.copy_(v)
+        graph.replay()
+        torch.cuda.synchronize()
+        want = ops.disentangled_attention(q, k, v, pk, pq, **kw)
+        torch.cuda.synchronize()
+        assert torch.equal(out_static, want)
+    ops.check_status()
+
+
 def test_unsupported_inputs_raise():
     from flashdeberta_b200 import _lib
     ops = _ops()
