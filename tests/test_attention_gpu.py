@@ -264,24 +264,26 @@ def test_fused_position_variants(c2p, p2c, buckets, max_rel):
 @pytest.mark.parametrize("c2p,p2c", [(True, True), (True, False), (False, True)])
 @pytest.mark.parametrize("packed", [False, True])
 @pytest.mark.parametrize("far", ["1", "2"])
-def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c, packed, far):
+@pytest.mark.parametrize("buckets,max_rel", [(256, 512), (32, 64), (-1, 96)])
+def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c, packed, far, buckets, max_rel):
     """Sequences long enough to have saturated key tiles on both sides of the band, run with the far key tiles in the
     two-team kernel and the band tiles in a second launch (forced through FDB_ATTN_SPLIT, which the library reads on
     every call; long calls take this path by themselves), against the single launch and the CPU oracle."""
     ops = _ops()
-    H, D, buckets, max_rel = 2, 64, 256, 512
+    H, D = 2, 64
+    span = buckets if buckets > 0 else max_rel
     lens = [1900, 130, 1, 1409, 2048]
     L = max(lens)
     sm = oracle.sm_scale_for(D, c2p, p2c)
     if packed:
-        q, k, v, pk, pq = _random(11, (sum(lens),), H, 256, c2p, p2c)
+        q, k, v, pk, pq = _random(11, (sum(lens),), H, span, c2p, p2c)
         cu = [0]
         for n in lens:
             cu.append(cu[-1] + n)
         starts = cu[:-1]
         kw = dict(cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV), max_seqlen=L)
     else:
-        q, k, v, pk, pq = _random(12, (len(lens), L), H, 256, c2p, p2c)
+        q, k, v, pk, pq = _random(12, (len(lens), L), H, span, c2p, p2c)
         starts = [b * L for b in range(len(lens))]
         kw = dict(seq_lens=torch.tensor(lens, dtype=torch.int32, device=DEV), max_seqlen=L)
     to = lambda t: None if t is None else t.to(DEV)
