@@ -45,7 +45,7 @@ class AttnParams(C.Structure):
 EXPORTS = (
     "fdb_abi_version", "fdb_last_error", "fdb_status_string", "fdb_build_bucket_lut", "fdb_relative_index",
     "fdb_attn_workspace_bytes", "fdb_attn_fwd", "fdb_attn_fwd_static", "fdb_attn_fwd_check", "fdb_relative_index_matrix",
-    "fdb_quantize_e4m3", "fdb_add_layernorm",
+    "fdb_quantize_e4m3", "fdb_add_layernorm", "fdb_linear_gelu",
 )
 
 _lib = None
@@ -93,6 +93,9 @@ def load() -> C.CDLL:
     lib.fdb_add_layernorm.restype = C.c_int
     lib.fdb_add_layernorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                       C.c_float, C.c_void_p]
+    lib.fdb_linear_gelu.restype = C.c_int
+    lib.fdb_linear_gelu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                    C.c_void_p, C.c_void_p]
     if lib.fdb_abi_version() != ABI_VERSION:
         raise RuntimeError(f"libfdb_b200.so has ABI {lib.fdb_abi_version()}, this package expects {ABI_VERSION}: rebuild")
     _lib = lib

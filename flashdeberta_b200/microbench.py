@@ -9,6 +9,10 @@ sequence and head).
     python -m flashdeberta_b200.microbench --add-layernorm --rows 16384 --hidden 768
 
 times the fused residual + LayerNorm kernel instead (algorithmic bytes: 3 * rows * hidden * 2, four rotated buffers).
+
+    python -m flashdeberta_b200.microbench --linear-gelu --rows 16384 --hidden 768 --out-features 3072
+
+times the fused linear + GELU kernel (2 * rows * hidden * out_features FLOP) beside torch's linear followed by gelu.
 """
 from __future__ import annotations
 
@@ -49,6 +53,34 @@ def bench_add_layernorm(rows: int, hidden: int, iters: int, warmup: int, sets: i
                       "l2": f"{sets} buffer sets rotated ({sets * 3 * rows * hidden * 2 >> 20} MiB; the output is allocated per call)"}))
 
 
+def bench_linear_gelu(rows: int, k: int, n: int, iters: int, warmup: int, sets: int):
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(0)
+    xs = [torch.randn(rows, k, generator=g).bfloat16().to(dev) for _ in range(sets)]
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(dev)
+    b = torch.randn(n, generator=g).bfloat16().to(dev)
+    F = torch.nn.functional
+    res = {}
+    for name, fn in (("fused", lambda x: ops.linear_gelu(x, w, b)), ("torch", lambda x: F.gelu(F.linear(x, w, b)))):
+        for i in range(warmup):
+            fn(xs[i % sets])
+        torch.cuda.synchronize()
+        times = []
+        for i in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(xs[i % sets])
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        res[name] = statistics.median(times)
+    ops.check_status()
+    flops = 2 * rows * k * n
+    print(json.dumps({"op": "linear_gelu", "rows": rows, "in_features": k, "out_features": n, "ms_median": res["fused"],
+                      "tflops_median": flops / res["fused"] / 1e9, "torch_linear_then_gelu_ms": res["torch"],
+                      "flops": flops, "l2": f"{sets} input buffers rotated; the output is allocated per call"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=8)
@@ -61,9 +93,13 @@ def main():
     ap.add_argument("--fp8", action="store_true", help="e4m3 operands (quantised once, outside the timed region)")
     ap.add_argument("--valid", type=int, default=0, help="valid length of every sequence (default: all)")
     ap.add_argument("--add-layernorm", action="store_true", help="time fdb_add_layernorm instead of the attention")
+    ap.add_argument("--linear-gelu", action="store_true", help="time fdb_linear_gelu (rows x hidden -> out-features)")
+    ap.add_argument("--out-features", type=int, default=3072)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--hidden", type=int, default=768)
     args = ap.parse_args()
+    if args.linear_gelu:
+        return bench_linear_gelu(args.rows, args.hidden, args.out_features, args.iters, args.warmup, args.sets)
     if args.add_layernorm:
         return bench_add_layernorm(args.rows, args.hidden, args.iters, args.warmup, max(args.sets, 8))
     dev = torch.device("cuda")

@@ -30,6 +30,7 @@ from transformers.models.deberta_v2.modeling_deberta_v2 import (
     DebertaV2ForQuestionAnswering,
     DebertaV2ForSequenceClassification,
     DebertaV2ForTokenClassification,
+    DebertaV2Intermediate,
     DebertaV2Layer,
     DebertaV2Model,
     DebertaV2Output,
@@ -89,6 +90,23 @@ class FlashDebertaV2Output(DebertaV2Output):
         return _dense_add_layernorm(self, hidden_states, input_tensor)
 
 
+class FlashDebertaV2Intermediate(DebertaV2Intermediate):
+    """Same parameters as transformers' block (the reference keeps it inside FlashDebertaV2Layer,
+    src/flashdeberta/model.py:265-272); dense and erf GELU run as one kernel when the case allows it (inference, CUDA,
+    bf16, hidden_act "gelu")."""
+
+    def __init__(self, config):
+        super().__init__(config)
+        self._erf_gelu = config.hidden_act == "gelu"
+
+    def forward(self, hidden_states):
+        d = self.dense
+        if (self._erf_gelu and not self.training and not torch.is_grad_enabled()
+                and ops.can_fuse_linear_gelu(hidden_states, d.weight, d.bias)):
+            return ops.linear_gelu(hidden_states, d.weight, d.bias)
+        return super().forward(hidden_states)
+
+
 class FlashDebertaV2Attention(DebertaV2Attention):
     def __init__(self, config):
         super().__init__(config)
@@ -102,6 +120,7 @@ class FlashDebertaV2Layer(DebertaV2Layer):
         super().__init__(config)
         self.attention = FlashDebertaV2Attention(config)
         if _backend(config) != "eager":
+            self.intermediate = FlashDebertaV2Intermediate(config)
             self.output = FlashDebertaV2Output(config)
 
 

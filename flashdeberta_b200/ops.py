@@ -18,7 +18,7 @@ import torch
 from . import _lib, bucket
 
 __all__ = [
-    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3", "add_layernorm", "can_fuse_add_layernorm",
+    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3", "add_layernorm", "can_fuse_add_layernorm", "linear_gelu", "can_fuse_linear_gelu",
     "check_status", "launch_count",
 ]
 
@@ -359,6 +359,36 @@ def add_layernorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: tor
                                          x2.shape[0], hidden, float(eps), C.c_void_p(stream)))
         _launches += 1
     return out.view(x.shape)
+
+
+def can_fuse_linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:
+    """True when ``linear_gelu`` can take the call: CUDA bf16, in_features a multiple of 64, out_features of 256."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.device == x.device
+            and weight.dim() == 2 and x.shape[-1] == weight.shape[1] and weight.shape[1] % 64 == 0
+            and weight.shape[0] % 256 == 0 and weight.is_contiguous()
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.device == x.device and bias.is_contiguous()
+                                  and bias.numel() == weight.shape[0])))
+
+
+def linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """GELU(x @ weight.T + bias) in one kernel (``fdb_linear_gelu``): the intermediate block of a layer, transformers'
+    DebertaV2Intermediate, which the reference's layer class keeps (src/flashdeberta/model.py:265-272).  erf GELU, the
+    sum rounded to bf16 before the activation as the two separate kernels would."""
+    global _launches
+    if not can_fuse_linear_gelu(x, weight, bias):
+        raise ValueError("linear_gelu needs CUDA bf16 tensors, in_features a multiple of 64 and out_features of 256")
+    lib = _lib.load()
+    k, n = weight.shape[1], weight.shape[0]
+    x2 = x.reshape(-1, k)
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    out = torch.empty(x2.shape[0], n, dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        _lib.check(lib.fdb_linear_gelu(x2.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                       out.data_ptr(), x2.shape[0], k, n, _status_word(x.device).data_ptr(),
+                                       C.c_void_p(stream)))
+        _launches += 1
+    return out.view(*x.shape[:-1], n)
 
 
 # --------------------------------------------------------------------------------------------------------------------

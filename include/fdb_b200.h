@@ -213,6 +213,19 @@ FDB_API int fdb_quantize_e4m3(const void* x_bf16, int64_t row_stride, int64_t he
 FDB_API int fdb_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                               int64_t rows, int32_t hidden, float eps, void* stream);
 
+/*
+ * out = GELU(x . weight^T + bias), erf form, bf16 in and out, fp32 accumulation in tensor memory; the sum is rounded to bf16
+ * before the activation, as the separate GEMM would leave it.  Replaces the intermediate block of an encoder layer, which
+ * the reference inherits from transformers (DebertaV2Intermediate: dense + ACT2FN["gelu"], inside FlashDebertaV2Layer,
+ * src/flashdeberta/model.py:265-272) — there a GEMM and an elementwise kernel with the (rows, out_features) activation
+ * written and read back in between, here one kernel.  x: (rows, in_features) contiguous; weight: (out_features,
+ * in_features) contiguous, the layout of torch.nn.Linear; bias: (out_features) or NULL; out: (rows, out_features).
+ * in_features a multiple of 64, out_features a multiple of 256, every pointer 16-byte aligned.  status: device word that
+ * receives FDB_DEV_TIMEOUT if a wait inside the kernel gives up (may be NULL).
+ */
+FDB_API int fdb_linear_gelu(const void* x, const void* weight, const void* bias, void* out, int64_t rows,
+                            int32_t in_features, int32_t out_features, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

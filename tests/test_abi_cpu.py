@@ -175,3 +175,23 @@ def test_layer_output_blocks_keep_transformers_parameter_names():
     with torch.no_grad():
         assert torch.equal(ours.output(h, x), theirs.output(h, x))
         assert torch.equal(ours.attention.output(x, x), theirs.attention.output(x, x))
+        assert torch.equal(ours.intermediate(x), theirs.intermediate(x))
+
+
+@pytest.mark.parametrize("x,weight,k,n,code", [
+    (0, 0x1000, 768, 3072, -1),        # x NULL
+    (0x1000, 0, 768, 3072, -1),        # weight NULL
+    (0x1000, 0x1000, 100, 3072, -2),   # in_features not a multiple of 64
+    (0x1000, 0x1000, 768, 1000, -2),   # out_features not a multiple of 256
+    (0x1008, 0x1000, 768, 3072, -3),   # x not 16-byte aligned
+])
+def test_linear_gelu_argument_errors(x, weight, k, n, code):
+    lib = _lib.load()
+    rc = lib.fdb_linear_gelu(x or None, weight or None, None, 0x2000, 4, k, n, None, None)
+    assert rc == code
+    assert lib.fdb_last_error().decode() != ""
+
+
+def test_linear_gelu_zero_rows_is_a_no_op():
+    lib = _lib.load()
+    assert lib.fdb_linear_gelu(0x1000, 0x1000, None, 0x2000, 0, 768, 3072, None, None) == 0

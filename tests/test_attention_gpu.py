@@ -570,6 +570,64 @@ def test_add_layernorm_rejects_what_it_does_not_cover():
         ops.add_layernorm(x32, None, w, w, 1e-7)
 
 
+@pytest.mark.parametrize("rows,k,n,with_bias", [(128, 64, 256, True), (5, 64, 256, True), (300, 128, 512, False),
+                                                (1000, 1024, 4096, True), (16384, 768, 3072, True), (0, 768, 3072, True)])
+def test_linear_gelu_vs_fp32_and_torch(rows, k, n, with_bias):
+    """fdb_linear_gelu against an fp32 restatement of gelu(bf16(x W^T + b)) and against torch's own bf16 linear + erf GELU
+    (same rounding points: equal almost everywhere, never more than one bf16 ulp of the result apart)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(rows + k + n)
+    x = torch.randn(rows, k, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(DEV)
+    b = (torch.randn(n, generator=g) * 0.5).bfloat16().to(DEV) if with_bias else None
+    out = ops.linear_gelu(x, w, b)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert out.shape == (rows, n) and out.dtype == torch.bfloat16
+    if rows == 0:
+        return
+    F = torch.nn.functional
+    want = F.gelu(F.linear(x.float(), w.float(), b.float() if with_bias else None).bfloat16().float())
+    err = (out.float() - want).abs()
+    # the sum itself is only known to one bf16 ulp (fp32 accumulation order), the result to one more
+    assert err.max().item() <= 6.3e-2 and err.mean().item() <= 2e-3, (err.max().item(), err.mean().item())
+    tref = F.gelu(F.linear(x, w, b))
+    diff = (out.float() - tref.float()).abs()
+    assert diff.max().item() <= 6.3e-2 and (diff > 0).float().mean().item() < 0.02, \
+        (diff.max().item(), (diff > 0).float().mean().item())
+
+
+def test_linear_gelu_values_across_the_range():
+    """The erfc form of GELU at the magnitudes where it could go wrong: large negative (result -> -0), large positive
+    (result -> v), around zero, +-inf from an overflowing sum stays as torch has it."""
+    ops = _ops()
+    vals = torch.tensor([-40., -12., -6., -3., -1., -0.25, -1e-3, 0., 1e-3, 0.25, 1., 3., 6., 12., 40., 300.])
+    k, n = 64, 256
+    x = torch.zeros(vals.numel(), k)
+    x[:, 0] = vals
+    w = torch.zeros(n, k)
+    w[:, 0] = 1.0
+    out = ops.linear_gelu(x.bfloat16().to(DEV), w.bfloat16().to(DEV), None)
+    torch.cuda.synchronize()
+    want = torch.nn.functional.gelu(vals.bfloat16().float())
+    got = out[:, 0].float().cpu()
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, rtol=8e-3, atol=1e-6), (got, want)
+    assert (out.float().cpu() == got[:, None]).all()  # every column saw the same sum
+
+
+def test_linear_gelu_rejects_what_it_does_not_cover():
+    ops = _ops()
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(256, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        ops.linear_gelu(x, w, None)
+    x = torch.zeros(4, 128, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(100, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        ops.linear_gelu(x, w, None)
+
+
 def test_call_can_be_captured_in_a_cuda_graph_and_replayed():
     """No host synchronisation, no allocation inside the library: a call (set-up kernels + fused kernel) is capturable;
     the replay on new inputs matches a direct call bit for bit."""
