@@ -352,6 +352,8 @@ def add_layernorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: tor
         r2 = residual.reshape(-1, hidden)
         r2 = r2 if r2.is_contiguous() else r2.contiguous()
     out = torch.empty_like(x2)
+    if x2.shape[0] == 0:
+        return out.view(x.shape)
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream(x.device).cuda_stream
         _lib.check(lib.fdb_add_layernorm(x2.data_ptr(), r2.data_ptr() if r2 is not None else None,
@@ -382,6 +384,8 @@ def linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     x2 = x.reshape(-1, k)
     x2 = x2 if x2.is_contiguous() else x2.contiguous()
     out = torch.empty(x2.shape[0], n, dtype=torch.bfloat16, device=x.device)
+    if x2.shape[0] == 0:
+        return out.view(*x.shape[:-1], n)
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream(x.device).cuda_stream
         _lib.check(lib.fdb_linear_gelu(x2.data_ptr(), weight.data_ptr(), bias.data_ptr() if bias is not None else None,
