@@ -14,7 +14,8 @@ FDB_OK = 0
 FDB_BF16, FDB_FP32, FDB_E4M3 = 0, 1, 2
 FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN = 1, 2
 STATIC_SCRATCH_BYTES = 8 << 20
-ABI_VERSION = 1
+ABI_VERSION = 2
+PREPARED_SCHEDULE, PREPARED_TABLES = 1, 2  # fdb_attn_params.prepared
 
 
 class AttnParams(C.Structure):
@@ -39,6 +40,7 @@ class AttnParams(C.Structure):
         ("lse", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
         ("status", C.c_void_p),
+        ("prepared", C.c_uint32),
     ]
 
 

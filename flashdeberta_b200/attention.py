@@ -83,6 +83,7 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         self._pos_cache = None
+        self._prepared = ops.PreparedWorkspace()  # this module's workspace: gathered tables and tile order are kept
         config = args[0] if args else kwargs.get("config")
         # FP8-e4m3 attention (per-head amax scales); a new switch, the reference has no FP8 path
         self.attn_fp8 = bool(getattr(config, "attn_fp8", False))
@@ -149,9 +150,13 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         if isinstance(attention_mask, PackedSequences):
             # packed tokens: hidden_states is (1, T, hidden); every sequence is addressed through cu_seqlens
             pk = attention_mask
-            fn = ops.disentangled_attention_fp8 if self.attn_fp8 else ops.disentangled_attention
-            out = fn(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query, cu_seqlens=pk.cu_seqlens,
-                     max_seqlen=pk.max_seqlen, sm_scale=sm_scale, position_buckets=buckets, max_relative_positions=max_rel)
+            kw = dict(cu_seqlens=pk.cu_seqlens, max_seqlen=pk.max_seqlen, sm_scale=sm_scale, position_buckets=buckets,
+                      max_relative_positions=max_rel)
+            if self.attn_fp8:
+                out = ops.disentangled_attention_fp8(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query, **kw)
+            else:
+                out = ops.disentangled_attention(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query,
+                                                 prepared=self._prepared, **kw)
             out = out.view(B, L, H * D)
             return (out if in_dtype == torch.bfloat16 else out.to(in_dtype), None)
         seq_lens = lengths_from_mask(attention_mask)
@@ -159,8 +164,12 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
             out = ops.disentangled_attention_fp8(q, k, v, pos_key, pos_query, seq_lens=seq_lens, max_seqlen=L,
                                                  sm_scale=sm_scale, position_buckets=buckets,
                                                  max_relative_positions=max_rel)
-        else:
+        elif torch.compiler.is_compiling():
             out = ops.attn_fwd_op(q, k, v, pos_key, pos_query, None, seq_lens, L, sm_scale, buckets, max_rel)
+        else:
+            out = ops.disentangled_attention(q, k, v, pos_key, pos_query, seq_lens=seq_lens, max_seqlen=L,
+                                             sm_scale=sm_scale, position_buckets=buckets,
+                                             max_relative_positions=max_rel, prepared=self._prepared)
         out = out.view(B, L, H * D)
         if in_dtype != torch.bfloat16:
             out = out.to(in_dtype)

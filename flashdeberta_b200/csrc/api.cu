@@ -41,6 +41,8 @@ int validate(const fdb_attn_params* p, bool fused) {
     return fail(FDB_ERR_INVALID_ARGUMENT, "dense layout needs total_rows == batch * max_seqlen (%d != %d * %d)",
                 p->total_rows, p->batch, p->max_seqlen);
   if (!(p->sm_scale > 0.f)) return fail(FDB_ERR_INVALID_ARGUMENT, "sm_scale must be positive");
+  if ((p->prepared & ~(FDB_PREPARED_SCHEDULE | FDB_PREPARED_TABLES)) != 0)
+    return fail(FDB_ERR_INVALID_ARGUMENT, "unknown bits in prepared: 0x%x", p->prepared);
   if (p->pos_key != nullptr || p->pos_query != nullptr) {
     const int span = p->position_buckets > 0 ? p->position_buckets : p->max_relative_positions;
     if (span <= 0) return fail(FDB_ERR_INVALID_ARGUMENT, "position tables given but att_span is %d", span);

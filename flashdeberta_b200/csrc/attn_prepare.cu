@@ -197,13 +197,14 @@ __global__ void expand_tables_kernel(const uint4* __restrict__ pos_key, const ui
 int launch_prepare(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(p.workspace);
-  seq_info_kernel<<<1, kScanThreads, 0, s>>>(p.cu_seqlens, p.seq_lens, p.batch, p.max_seqlen, p.total_rows,
-                                             reinterpret_cast<int32_t*>(ws + w.seq_info),
-                                             reinterpret_cast<int32_t*>(ws + w.tile_first),
-                                             reinterpret_cast<int4*>(ws + w.slot_info), (int)tile_slots(p), p.status);
+  if ((p.prepared & FDB_PREPARED_SCHEDULE) == 0)
+    seq_info_kernel<<<1, kScanThreads, 0, s>>>(p.cu_seqlens, p.seq_lens, p.batch, p.max_seqlen, p.total_rows,
+                                               reinterpret_cast<int32_t*>(ws + w.seq_info),
+                                               reinterpret_cast<int32_t*>(ws + w.tile_first),
+                                               reinterpret_cast<int4*>(ws + w.slot_info), (int)tile_slots(p), p.status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "seq_info launch: %s", cudaGetErrorString(e));
-  if (p.pos_key != nullptr || p.pos_query != nullptr) {
+  if ((p.pos_key != nullptr || p.pos_query != nullptr) && (p.prepared & FDB_PREPARED_TABLES) == 0) {
     const int esz = p.dtype == FDB_E4M3 ? 1 : 2;
     const int vec_per_row = kHeadDim * esz / 16;
     const int table_rows = 2 * (p.position_buckets > 0 ? p.position_buckets : p.max_relative_positions);

@@ -162,6 +162,8 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         if (getattr(self.config_pack, "pack_sequences", True) and self.conv is None and query_states is None
                 and torch.is_tensor(hidden_states) and input_mask.dim() == 2):
             packed = PackedSequences.from_mask(input_mask)
+            if packed is None:
+                seq_lens = None  # no padding anywhere (from_mask has looked): the layers' tile order can be kept
         if packed is not None:
             return self._forward_packed(hidden_states, packed, output_hidden_states, return_dict)
 

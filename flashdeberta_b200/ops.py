@@ -19,7 +19,7 @@ from . import _lib, bucket
 
 __all__ = [
     "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3", "add_layernorm", "can_fuse_add_layernorm", "linear_gelu", "can_fuse_linear_gelu",
-    "check_status", "launch_count",
+    "check_status", "launch_count", "PreparedWorkspace",
 ]
 
 _status: Dict[str, torch.Tensor] = {}
@@ -149,12 +149,29 @@ def _out_like(q: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return torch.empty(q.shape, dtype=dtype, device=q.device)
 
 
+class PreparedWorkspace:
+    """A workspace that one caller (an attention module) keeps between calls, so that what the set-up kernels wrote into
+    it can be used again (``fdb_attn_params.prepared``): the position tables gathered through the bucket index as long
+    as the same table tensors come back unmodified, the order of the query tiles as long as the batch has the same shape
+    and no padding.  Workspaces above ``max_bytes`` (long sequences in two launches: partial results per row) are not
+    kept; such calls take a fresh scratch buffer as without this object."""
+
+    max_bytes = 64 << 20
+
+    def __init__(self):
+        self.buf = None
+        self.layout = None     # everything the workspace layout and the schedule depend on
+        self.schedule = False  # the schedule in `buf` is that of an unpadded batch of this layout
+        self.tables = None     # (data_ptr, version) of the table tensors gathered into `buf`
+        self.keep = None       # those tensors, so that their addresses stay theirs
+
+
 def disentangled_attention(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     pos_key: Optional[torch.Tensor], pos_query: Optional[torch.Tensor],
     *, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
     max_seqlen: int, sm_scale: Optional[float] = None, position_buckets: int = -1, max_relative_positions: int = -1,
-    return_lse: bool = False, scales: Optional[dict] = None,
+    return_lse: bool = False, scales: Optional[dict] = None, prepared: Optional[PreparedWorkspace] = None,
 ):
     """softmax((Q K^T + c2p + p2c) * sm_scale) V on the fused sm_100a kernel.
 
@@ -179,10 +196,26 @@ def disentangled_attention(
         if need == 0:  # invalid parameters (raises with the library's message) or an empty batch
             _lib.check(lib.fdb_attn_fwd(C.byref(p), None))
             return (out, lse) if return_lse else out
-        ws = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
-        base = (ws.data_ptr() + 255) & ~255
-        p.workspace, p.workspace_bytes = base, need
         stream = torch.cuda.current_stream(q.device).cuda_stream
+        flags = 0
+        if prepared is not None and need <= prepared.max_bytes:
+            layout = (q.device, stream, need, p.dtype, p.batch, p.max_seqlen, p.total_rows, p.heads, int(position_buckets),
+                      int(max_relative_positions), cu_seqlens is not None)
+            tables = tuple((t.data_ptr(), t._version) if t is not None else None for t in (pos_key, pos_query))
+            full = cu_seqlens is None and seq_lens is None
+            if prepared.buf is None or prepared.layout != layout:
+                prepared.buf = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
+            else:
+                if full and prepared.schedule:
+                    flags |= _lib.PREPARED_SCHEDULE
+                if prepared.tables == tables and tables != (None, None):
+                    flags |= _lib.PREPARED_TABLES
+            prepared.layout, prepared.schedule, prepared.tables, prepared.keep = None, False, None, None
+            ws = prepared.buf
+        else:
+            ws = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
+        base = (ws.data_ptr() + 255) & ~255
+        p.workspace, p.workspace_bytes, p.prepared = base, need, flags
         if event_log is not None:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
@@ -190,7 +223,10 @@ def disentangled_attention(
         if event_log is not None:
             ev1.record()
             event_log.append((ev0, ev1))
-        _launches += 2 + int(pos_key is not None or pos_query is not None)
+        if prepared is not None and ws is prepared.buf:  # the call went through: the workspace holds this call's set-up
+            prepared.layout, prepared.schedule, prepared.tables, prepared.keep = layout, full, tables, (pos_key, pos_query)
+        _launches += 1 + int(not flags & _lib.PREPARED_SCHEDULE) + \
+            int((pos_key is not None or pos_query is not None) and not flags & _lib.PREPARED_TABLES)
         # `keep` and `ws` were allocated on this stream, so the caching allocator reuses them in stream order
         del keep, ws
     return (out, lse) if return_lse else out

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define FDB_ABI_VERSION 1
+#define FDB_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define FDB_API __attribute__((visibility("default")))
@@ -118,7 +118,21 @@ typedef struct fdb_attn_params {
   uint64_t workspace_bytes;
 
   int32_t* status; /* device int32, OR-ed with FDB_DEV_* bits; may be NULL */
+
+  /* FDB_PREPARED_* bits (fdb_attn_fwd only): what the workspace still holds from an earlier fdb_attn_fwd call on it, so
+   * that the set-up kernel that writes it is not launched again.  FDB_PREPARED_SCHEDULE: the per-sequence rows and the
+   * order of the query tiles — valid while batch, max_seqlen, total_rows and the contents of cu_seqlens / seq_lens are
+   * the same.  FDB_PREPARED_TABLES: the position tables gathered through the bucket index — valid while pos_key,
+   * pos_query (pointers and contents), heads, dtype and the bucket settings are the same.  Both also need the same
+   * workspace size as the call that wrote them (same fdb_attn_workspace_bytes), and nothing else may have used the
+   * workspace in between.  The reference recomputes both for every layer of every forward (the tile map in a host loop,
+   * flash_attention_varlen.py:71-83; the index arithmetic per score element, flash_attention.py:236-254).  0: nothing
+   * is assumed. */
+  uint32_t prepared;
 } fdb_attn_params;
+
+#define FDB_PREPARED_SCHEDULE 1u
+#define FDB_PREPARED_TABLES 2u
 
 /* Library / ABI version (FDB_ABI_VERSION the library was built with). */
 FDB_API int fdb_abi_version(void);

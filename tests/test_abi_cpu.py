@@ -101,6 +101,7 @@ def _params(**kw):
     (dict(sm_scale=0.0), -1),
     (dict(pos_key=0x2000), -1),       # tables without a bucket table
     (dict(seq_lens=0x10, cu_seqlens=0x10), -1),
+    (dict(prepared=4), -1),           # unknown bit
 ])
 def test_argument_errors_are_reported_before_any_launch(change, code):
     lib = _lib.load()

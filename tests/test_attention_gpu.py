@@ -628,6 +628,71 @@ def test_linear_gelu_rejects_what_it_does_not_cover():
         ops.linear_gelu(x, w, None)
 
 
+def test_prepared_workspace_reuse_matches_fresh_calls():
+    """A workspace kept between calls (fdb_attn_params.prepared): the second call on the same tables and an unpadded
+    batch of the same shape launches the fused kernel alone and gives the same bits; a table modified in place, a
+    padded batch, another shape and a packed batch each fall back to as much set-up as they need."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(11)
+    B, L, H, D = 2, 384, 4, 64
+    kw = dict(position_buckets=32, max_relative_positions=64)
+
+    def rnd(*shape):
+        return torch.randn(*shape, generator=g).bfloat16().to(DEV)
+
+    q, k, v = rnd(B, L, H, D), rnd(B, L, H, D), rnd(B, L, H, D)
+    pk, pq = rnd(H, 64, D), rnd(H, 64, D)
+    prepared = ops.PreparedWorkspace()
+    fresh = ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, **kw)
+    n0 = ops.launch_count()
+    first = ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, prepared=prepared, **kw)
+    n1 = ops.launch_count()
+    second = ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, prepared=prepared, **kw)
+    n2 = ops.launch_count()
+    assert (n1 - n0, n2 - n1) == (3, 1)
+    assert torch.equal(first, fresh) and torch.equal(second, fresh)
+
+    q2 = rnd(B, L, H, D)  # other inputs, same shape: still nothing to set up
+    n0 = ops.launch_count()
+    out = ops.disentangled_attention(q2, k, v, pk, pq, max_seqlen=L, prepared=prepared, **kw)
+    assert ops.launch_count() - n0 == 1
+    assert torch.equal(out, ops.disentangled_attention(q2, k, v, pk, pq, max_seqlen=L, **kw))
+
+    pk.mul_(0.5)  # a table changed in place: gathered again, the tile order is kept
+    n0 = ops.launch_count()
+    out = ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, prepared=prepared, **kw)
+    assert ops.launch_count() - n0 == 2
+    assert torch.equal(out, ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, **kw))
+    assert not torch.equal(out, fresh)
+
+    lens = torch.tensor([L, 100], dtype=torch.int32, device=DEV)  # padding: the tile order is computed again
+    n0 = ops.launch_count()
+    out = ops.disentangled_attention(q, k, v, pk, pq, seq_lens=lens, max_seqlen=L, prepared=prepared, **kw)
+    assert ops.launch_count() - n0 == 2
+    assert torch.equal(out, ops.disentangled_attention(q, k, v, pk, pq, seq_lens=lens, max_seqlen=L, **kw))
+    n0 = ops.launch_count()
+    out = ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, prepared=prepared, **kw)  # and again for no padding
+    assert ops.launch_count() - n0 == 2
+    assert torch.equal(out, ops.disentangled_attention(q, k, v, pk, pq, max_seqlen=L, **kw))
+
+    qs, ks, vs = q[:, :256].contiguous(), k[:, :256].contiguous(), v[:, :256].contiguous()  # another shape: all of it
+    n0 = ops.launch_count()
+    out = ops.disentangled_attention(qs, ks, vs, pk, pq, max_seqlen=256, prepared=prepared, **kw)
+    assert ops.launch_count() - n0 == 3
+    assert torch.equal(out, ops.disentangled_attention(qs, ks, vs, pk, pq, max_seqlen=256, **kw))
+
+    cu = torch.tensor([0, 300, 500], dtype=torch.int32, device=DEV)  # packed: tables kept from the second call on
+    qp, kp, vp = rnd(500, H, D), rnd(500, H, D), rnd(500, H, D)
+    want = ops.disentangled_attention(qp, kp, vp, pk, pq, cu_seqlens=cu, max_seqlen=300, **kw)
+    for expect in (3, 2):
+        n0 = ops.launch_count()
+        out = ops.disentangled_attention(qp, kp, vp, pk, pq, cu_seqlens=cu, max_seqlen=300, prepared=prepared, **kw)
+        assert ops.launch_count() - n0 == expect
+        assert torch.equal(out, want)
+    torch.cuda.synchronize()
+    ops.check_status()
+
+
 def test_call_can_be_captured_in_a_cuda_graph_and_replayed():
     """No host synchronisation, no allocation inside the library: a call (set-up kernels + fused kernel) is capturable;
     the replay on new inputs matches a direct call bit for bit."""
