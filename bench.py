@@ -295,7 +295,7 @@ def gpu_arm(args):
         "roofline": {"kernel": "attn_fwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
                      "unit": "TFLOP/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                      "launch_ms": attn_avg_ms, "flops_per_launch": f_launch,
-                     "note": "events bracket one fdb_attn_fwd call (set-up kernels + fused kernel)"},
+                     "note": "events bracket one fdb_attn_fwd call (the fused kernel; its two set-up kernels run only while a module's workspace is not prepared)"},
         "attention_share_of_step": attn_avg_ms * 12 / ms_step,
         "model_tflops": total_flops / (ms_step / 1e3) / 1e12,
     }
