@@ -1,8 +1,14 @@
 // Per-slab amax scaling of bf16 rows to float8 e4m3 (the FP8 option; the reference has no FP8 code).
 //
-// One CTA per (slab, head).  A slab is a run of rows [slab_start[s], slab_start[s+1]) — one sequence, or the whole
-// position table — so every (sequence, head) gets its own scale = amax/448 and the stored value times the scale gives
-// the input back.
+// A slab is a run of rows [slab_start[s], slab_start[s+1]) — one sequence, or the whole position table — and every
+// (slab, head) gets its own scale = amax/448, so the stored value times the scale gives the input back.
+// Three small kernels on the caller's stream, each with enough CTAs to fill the GPU whatever the number of slabs (one CTA
+// per (slab, head), the first form of this file, left 8 x 16 = 128 CTAs to stream 100 MB):
+//   amax_kernel      a CTA takes 64-row chunks of one slab, all heads; eight lanes share a (row, head), reduce with
+//                    shuffles, then per head through shared memory into the scale array (bit pattern of a non-negative
+//                    float, so an unsigned atomicMax orders it)
+//   quantize_kernel  the same walk, x * 448/amax -> e4m3
+//   scale_kernel     amax -> amax/448 in place
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -13,44 +19,62 @@ namespace fdb {
 namespace {
 
 constexpr int kQuantThreads = 256;
+constexpr int kChunkRows = 64;
 
-__global__ void __launch_bounds__(kQuantThreads) quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, int64_t row_stride,
-                                                                      int64_t head_stride,
-                                                                      const int32_t* __restrict__ slab_start, int heads,
-                                                                      int head_dim, uint8_t* __restrict__ y,
-                                                                      float* __restrict__ scale) {
-  __shared__ float red[kQuantThreads / 32];
-  __shared__ float s_scale;
-  const int slab = blockIdx.x, h = blockIdx.y;
-  const int r0 = slab_start[slab], r1 = slab_start[slab + 1];
-  const int vec_per_row = head_dim / 8;  // 8 bf16 = 16 bytes
-  const int64_t n_vec = (int64_t)max(r1 - r0, 0) * vec_per_row;
-  float amax = 0.f;
-  for (int64_t i = threadIdx.x; i < n_vec; i += kQuantThreads) {
-    const int r = r0 + (int)(i / vec_per_row), c = (int)(i % vec_per_row);
-    const uint4 v = *reinterpret_cast<const uint4*>(x + r * row_stride + h * head_stride + c * 8);
-    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 f = __bfloat1622float2(b[k]);
-      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+// (row, head) pairs of rows [r0 + chunk * 64, ...) of the slab, eight lanes (16 bytes each) per pair
+template <typename F>
+__device__ __forceinline__ void walk_slab(const int32_t* __restrict__ slab_start, int heads, F&& body) {
+  const int slab = blockIdx.y;
+  const int r0 = slab_start[slab], len = max(slab_start[slab + 1] - r0, 0);
+  const int sub = threadIdx.x & 7;
+  for (int chunk = blockIdx.x; chunk * kChunkRows < len; chunk += gridDim.x) {
+    const int rows = min(kChunkRows, len - chunk * kChunkRows);
+    const int pairs = rows * heads;
+    for (int p = threadIdx.x >> 3; p < ((pairs + 31) & ~31); p += kQuantThreads >> 3) {  // whole warps stay together
+      const bool live = p < pairs;
+      const int r = r0 + chunk * kChunkRows + (live ? p / heads : 0), h = live ? p % heads : 0;
+      body(live, r, h, sub);
     }
   }
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+}
+
+__global__ void __launch_bounds__(kQuantThreads) amax_kernel(const __nv_bfloat16* __restrict__ x, int64_t row_stride,
+                                                             int64_t head_stride, const int32_t* __restrict__ slab_start,
+                                                             int heads, unsigned int* __restrict__ amax_bits) {
+  extern __shared__ unsigned int s_amax[];
+  for (int h = threadIdx.x; h < heads; h += kQuantThreads) s_amax[h] = 0u;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    float a = red[0];
-    for (int w = 1; w < kQuantThreads / 32; ++w) a = fmaxf(a, red[w]);
-    a = fmaxf(a, 1e-12f);
-    s_scale = a / 448.f;
-    scale[(int64_t)slab * heads + h] = s_scale;
-  }
+  walk_slab(slab_start, heads, [&](bool live, int r, int h, int sub) {
+    float a = 0.f;
+    if (live) {
+      const uint4 v = *reinterpret_cast<const uint4*>(x + r * row_stride + h * head_stride + sub * 8);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(b[k]);
+        a = fmaxf(a, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    if (live && sub == 0 && a > 0.f) atomicMax(&s_amax[h], __float_as_uint(a));
+  });
   __syncthreads();
-  const float inv = 1.f / s_scale;
-  for (int64_t i = threadIdx.x; i < n_vec; i += kQuantThreads) {
-    const int r = r0 + (int)(i / vec_per_row), c = (int)(i % vec_per_row);
-    const uint4 v = *reinterpret_cast<const uint4*>(x + r * row_stride + h * head_stride + c * 8);
+  for (int h = threadIdx.x; h < heads; h += kQuantThreads)
+    if (s_amax[h] != 0u) atomicMax(&amax_bits[(int64_t)blockIdx.y * heads + h], s_amax[h]);
+}
+
+__device__ __forceinline__ float scale_of(unsigned int amax_bits) { return fmaxf(__uint_as_float(amax_bits), 1e-12f) / 448.f; }
+
+__global__ void __launch_bounds__(kQuantThreads) quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t row_stride,
+                                                                 int64_t head_stride, const int32_t* __restrict__ slab_start,
+                                                                 int heads, uint8_t* __restrict__ y,
+                                                                 const unsigned int* __restrict__ amax_bits) {
+  walk_slab(slab_start, heads, [&](bool live, int r, int h, int sub) {
+    if (!live) return;
+    const float inv = 1.f / scale_of(amax_bits[(int64_t)blockIdx.y * heads + h]);
+    const uint4 v = *reinterpret_cast<const uint4*>(x + r * row_stride + h * head_stride + sub * 8);
     const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
     uint16_t o[4];
 #pragma unroll
@@ -61,18 +85,35 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_e4m3_kernel(const __nv
     uint2 packed;
     packed.x = (uint32_t)o[0] | ((uint32_t)o[1] << 16);
     packed.y = (uint32_t)o[2] | ((uint32_t)o[3] << 16);
-    *reinterpret_cast<uint2*>(y + ((int64_t)r * heads + h) * head_dim + c * 8) = packed;
-  }
+    *reinterpret_cast<uint2*>(y + ((int64_t)r * heads + h) * 64 + sub * 8) = packed;
+  });
+}
+
+__global__ void scale_kernel(float* __restrict__ scale, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) scale[i] = scale_of(__float_as_uint(scale[i]));
 }
 
 }  // namespace
 
 int launch_quantize_e4m3(const void* x, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
                          int32_t n_slabs, int32_t heads, int32_t head_dim, void* y, float* scale, void* stream) {
-  quantize_e4m3_kernel<<<dim3(n_slabs, heads), kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), row_stride, head_stride, slab_start, heads, head_dim,
-      static_cast<uint8_t*>(y), scale);
-  const cudaError_t e = cudaGetLastError();
+  if (head_dim != 64) return fail(FDB_ERR_UNSUPPORTED, "quantize_e4m3 is built for head_dim 64, got %d", head_dim);
+  if (n_slabs <= 0 || heads <= 0) return FDB_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int n = n_slabs * heads;
+  cudaError_t e = cudaMemsetAsync(scale, 0, sizeof(float) * n, s);
+  if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "quantize_e4m3 memset: %s", cudaGetErrorString(e));
+  // the slab lengths are on the device: a fixed number of CTAs per slab walks its 64-row chunks (about 1200 CTAs in all)
+  int per_slab = (1184 + n_slabs - 1) / n_slabs;
+  per_slab = per_slab < 1 ? 1 : (per_slab > 128 ? 128 : per_slab);
+  const dim3 grid(per_slab, n_slabs);
+  auto* xb = static_cast<const __nv_bfloat16*>(x);
+  auto* bits = reinterpret_cast<unsigned int*>(scale);
+  amax_kernel<<<grid, kQuantThreads, sizeof(unsigned int) * heads, s>>>(xb, row_stride, head_stride, slab_start, heads, bits);
+  quantize_kernel<<<grid, kQuantThreads, 0, s>>>(xb, row_stride, head_stride, slab_start, heads, static_cast<uint8_t*>(y), bits);
+  scale_kernel<<<(n + 255) / 256, 256, 0, s>>>(scale, n);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "quantize_e4m3 launch: %s", cudaGetErrorString(e));
   return FDB_OK;
 }

@@ -693,6 +693,42 @@ def test_prepared_workspace_reuse_matches_fresh_calls():
     ops.check_status()
 
 
+@pytest.mark.parametrize("lens,heads,strided", [([300, 0, 1, 77], 12, False), ([4096, 4096], 16, True), ([512] * 12, 1, False),
+                                                 ([65] * 40, 4, True)])
+def test_quantize_e4m3_scales_and_values(lens, heads, strided):
+    """fdb_quantize_e4m3: scale = amax/448 per (slab, head) (1e-12/448 for an empty or all-zero slab), values
+    = e4m3(x / scale), for ragged slabs, an empty one, many slabs, one head (the position tables) and a strided input."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(sum(lens) + heads)
+    rows, D = sum(lens), 64
+    if strided:  # q inside a (rows, 3, H, D) projection
+        base = (torch.randn(rows, 3, heads, D, generator=g) * 3).bfloat16().to(DEV)
+        x = base[:, 1]
+    else:
+        x = (torch.randn(rows, heads, D, generator=g) * 3).bfloat16().to(DEV)
+    start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    y, scale = ops.quantize_e4m3(x, start)
+    torch.cuda.synchronize()
+    assert y.shape == x.shape and y.dtype == torch.float8_e4m3fn and scale.shape == (len(lens), heads)
+    at = 0
+    for s, n in enumerate(lens):
+        blk = x[at:at + n].float()
+        amax = blk.abs().amax(dim=(0, 2)) if n > 0 else torch.zeros(heads, device=DEV)
+        want_scale = torch.clamp(amax, min=1e-12) / 448.0
+        assert torch.allclose(scale[s], want_scale, rtol=1e-6, atol=0), (s, scale[s], want_scale)
+        if n > 0:
+            got = y[at:at + n].float()
+            assert got.abs().amax().item() == 448.0  # the largest element of some head sits on the last code
+            # value * scale gives the input back to half an e4m3 step (3 mantissa bits; subnormal step 2^-9)
+            back = got * scale[s][None, :, None]
+            step = torch.maximum(blk.abs() * 2.0 ** -4, scale[s][None, :, None] * 2.0 ** -10)
+            assert ((back - blk).abs() <= step * 1.001).all()
+            # and the codes are torch's own for the same scale, up to the few that sit on a rounding boundary
+            want = (blk * (1.0 / scale[s])[None, :, None]).to(torch.float8_e4m3fn)
+            assert (y[at:at + n].view(torch.uint8) != want.view(torch.uint8)).float().mean().item() < 1e-3
+        at += n
+
+
 def test_call_can_be_captured_in_a_cuda_graph_and_replayed():
     """No host synchronisation, no allocation inside the library: a call (set-up kernels + fused kernel) is capturable;
     the replay on new inputs matches a direct call bit for bit."""
