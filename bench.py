@@ -361,12 +361,15 @@ def varlen_run(args):
             step()
         barrier()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ops.event_log = []
         t0.record()
         for _ in range(args.steps):
             out = step()
         t1.record()
         barrier()
         ms = t0.elapsed_time(t1)
+        attn_ms = sum(a.elapsed_time(b) for a, b in ops.event_log)  # rank 0's own fused-attention calls
+        ops.event_log = None
         if world > 1:
             t = torch.tensor([ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -383,7 +386,10 @@ def varlen_run(args):
             "config": {"workload": "varlen packed batch, DeBERTa-v3-large encoder, 256 sequences, lengths log-uniform in "
                                    "[64, 8192] (seed 2)", "total_tokens": total, "tokens_rank0": my_tokens,
                        "parallelism": f"dp{world}, sequences split by token count"},
-            "model_tflops": (f_attn + f_lin) / (ms / args.steps / 1e3) / 1e12}), flush=True)
+            "model_tflops": (f_attn + f_lin) / (ms / args.steps / 1e3) / 1e12,
+            "attention_share_of_step": attn_ms / ms,
+            "attention_tflops_rank0": 24 * attn_flops([lens[i] for i in mine], heads=16) * args.steps / (attn_ms / 1e3) / 1e12,
+        }), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
