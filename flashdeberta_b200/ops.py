@@ -164,6 +164,7 @@ class PreparedWorkspace:
         self.schedule = False  # the schedule in `buf` is that of an unpadded batch of this layout
         self.tables = None     # (data_ptr, version) of the table tensors gathered into `buf`
         self.keep = None       # those tensors, so that their addresses stay theirs
+        self.stream = None     # the stream whose order protects `buf`
 
 
 def disentangled_attention(
@@ -198,7 +199,8 @@ def disentangled_attention(
             return (out, lse) if return_lse else out
         stream = torch.cuda.current_stream(q.device).cuda_stream
         flags = 0
-        if prepared is not None and need <= prepared.max_bytes:
+        if prepared is not None and need <= prepared.max_bytes and prepared.stream in (None, stream):
+            prepared.stream = stream  # the buffer stays with the first stream that used it; other streams take scratch
             layout = (q.device, stream, need, p.dtype, p.batch, p.max_seqlen, p.total_rows, p.heads, int(position_buckets),
                       int(max_relative_positions), cu_seqlens is not None)
             tables = tuple((t.data_ptr(), t._version) if t is not None else None for t in (pos_key, pos_query))
