@@ -153,7 +153,7 @@ class PreparedWorkspace:
     """A workspace that one caller (an attention module) keeps between calls, so that what the set-up kernels wrote into
     it can be used again (``fdb_attn_params.prepared``): the position tables gathered through the bucket index as long
     as the same table tensors come back unmodified, the order of the query tiles as long as the batch has the same shape
-    and no padding.  Workspaces above ``max_bytes`` (long sequences in two launches: partial results per row) are not
+    and either no padding or the same, unmodified lengths tensor.  Workspaces above ``max_bytes`` (long sequences in two launches: partial results per row) are not
     kept; such calls take a fresh scratch buffer as without this object."""
 
     max_bytes = 64 << 20
@@ -161,7 +161,7 @@ class PreparedWorkspace:
     def __init__(self):
         self.buf = None
         self.layout = None     # everything the workspace layout and the schedule depend on
-        self.schedule = False  # the schedule in `buf` is that of an unpadded batch of this layout
+        self.schedule = None   # whose tile order `buf` holds: ("full",) for an unpadded batch, else (data_ptr, version) of the lengths tensor
         self.tables = None     # (data_ptr, version) of the table tensors gathered into `buf`
         self.keep = None       # those tensors, so that their addresses stay theirs
         self.stream = None     # the stream whose order protects `buf`
@@ -204,15 +204,17 @@ def disentangled_attention(
             layout = (q.device, stream, need, p.dtype, p.batch, p.max_seqlen, p.total_rows, p.heads, int(position_buckets),
                       int(max_relative_positions), cu_seqlens is not None)
             tables = tuple((t.data_ptr(), t._version) if t is not None else None for t in (pos_key, pos_query))
-            full = cu_seqlens is None and seq_lens is None
+            lens_t = cu_seqlens if cu_seqlens is not None else seq_lens
+            # the lengths behind the tile order: none (an unpadded batch), or this very tensor, unmodified
+            full = ("full",) if lens_t is None else (lens_t.data_ptr(), lens_t._version)
             if prepared.buf is None or prepared.layout != layout:
                 prepared.buf = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
             else:
-                if full and prepared.schedule:
+                if prepared.schedule == full:
                     flags |= _lib.PREPARED_SCHEDULE
                 if prepared.tables == tables and tables != (None, None):
                     flags |= _lib.PREPARED_TABLES
-            prepared.layout, prepared.schedule, prepared.tables, prepared.keep = None, False, None, None
+            prepared.layout, prepared.schedule, prepared.tables, prepared.keep = None, None, None, None
             ws = prepared.buf
         else:
             ws = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
@@ -226,7 +228,7 @@ def disentangled_attention(
             ev1.record()
             event_log.append((ev0, ev1))
         if prepared is not None and ws is prepared.buf:  # the call went through: the workspace holds this call's set-up
-            prepared.layout, prepared.schedule, prepared.tables, prepared.keep = layout, full, tables, (pos_key, pos_query)
+            prepared.layout, prepared.schedule, prepared.tables, prepared.keep = layout, full, tables, (pos_key, pos_query, lens_t)
         _launches += 1 + int(not flags & _lib.PREPARED_SCHEDULE) + \
             int((pos_key is not None or pos_query is not None) and not flags & _lib.PREPARED_TABLES)
         # `keep` and `ws` were allocated on this stream, so the caching allocator reuses them in stream order

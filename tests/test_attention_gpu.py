@@ -681,14 +681,16 @@ def test_prepared_workspace_reuse_matches_fresh_calls():
     assert ops.launch_count() - n0 == 3
     assert torch.equal(out, ops.disentangled_attention(qs, ks, vs, pk, pq, max_seqlen=256, **kw))
 
-    cu = torch.tensor([0, 300, 500], dtype=torch.int32, device=DEV)  # packed: tables kept from the second call on
+    cu = torch.tensor([0, 300, 500], dtype=torch.int32, device=DEV)  # packed: everything kept from the second call on
     qp, kp, vp = rnd(500, H, D), rnd(500, H, D), rnd(500, H, D)
     want = ops.disentangled_attention(qp, kp, vp, pk, pq, cu_seqlens=cu, max_seqlen=300, **kw)
-    for expect in (3, 2):
+    for expect in (3, 1, 2):  # new layout; the same lengths tensor again; the lengths tensor written to in between
         n0 = ops.launch_count()
         out = ops.disentangled_attention(qp, kp, vp, pk, pq, cu_seqlens=cu, max_seqlen=300, prepared=prepared, **kw)
         assert ops.launch_count() - n0 == expect
         assert torch.equal(out, want)
+        if expect == 1:
+            cu.add_(0)
     torch.cuda.synchronize()
     ops.check_status()
 
@@ -771,6 +773,61 @@ def test_unsupported_inputs_raise():
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="length"):
         ops.check_status()
+
+
+def test_model_repeated_calls_and_mask_changes():
+    """What the encoder and the attention modules keep between calls (mask analysis, gathered tables, tile order) never
+    outlives its inputs: the same mask tensor again, the mask written to in place, an unpadded mask, another shape and a
+    weight changed in place all give what a freshly built model gives."""
+    from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+    from flashdeberta_b200 import FlashDebertaV2Model
+    torch.manual_seed(1)
+    cfg = DebertaV2Config(vocab_size=500, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                          intermediate_size=512, relative_attention=True, position_buckets=32,
+                          max_relative_positions=64, pos_att_type="c2p|p2c", share_att_key=True,
+                          norm_rel_ebd="layer_norm", position_biased_input=False, type_vocab_size=0,
+                          layer_norm_eps=1e-7)
+    cfg.attn_backend = "b200"
+    model = FlashDebertaV2Model(cfg).eval().to(DEV).bfloat16()
+
+    def fresh(ids, mask):
+        other = FlashDebertaV2Model(cfg).eval()
+        other.load_state_dict(model.state_dict())
+        other = other.to(DEV).bfloat16()
+        with torch.no_grad():
+            return other(input_ids=ids, attention_mask=mask.clone()).last_hidden_state
+
+    def run(ids, mask):
+        with torch.no_grad():
+            return model(input_ids=ids, attention_mask=mask).last_hidden_state
+
+    B, L = 3, 300
+    ids = torch.randint(1, 500, (B, L), device=DEV)
+    mask = torch.ones(B, L, device=DEV)
+    first = run(ids, mask)
+    assert torch.equal(first, fresh(ids, mask))
+    assert torch.equal(run(ids, mask), first)          # everything kept
+    ids2 = torch.randint(1, 500, (B, L), device=DEV)
+    assert torch.equal(run(ids2, mask), fresh(ids2, mask))
+    mask[1, 120:] = 0                                  # same tensor, written to: padded now (runs packed)
+    padded = run(ids, mask)
+    assert torch.equal(padded, fresh(ids, mask))
+    assert torch.count_nonzero(padded[1, 120:]) == 0
+    assert torch.equal(run(ids, mask), padded)
+    mask[1, 120:] = 1                                  # and back
+    assert torch.equal(run(ids, mask), first)
+    ids3 = torch.randint(1, 500, (2, 200), device=DEV)  # another shape
+    mask3 = torch.ones(2, 200, device=DEV)
+    assert torch.equal(run(ids3, mask3), fresh(ids3, mask3))
+    with torch.no_grad():                              # a projection changed in place: new position tables
+        model.encoder.layer[0].attention.self.query_proj.weight.mul_(1.5)
+        model.encoder.rel_embeddings.weight.add_(0.01)
+    again = run(ids, mask)
+    assert torch.equal(again, fresh(ids, mask))
+    assert not torch.equal(again, first)
+    torch.cuda.synchronize()
+    from flashdeberta_b200 import ops
+    ops.check_status()
 
 
 def test_model_b200_backend_vs_eager_backend():
