@@ -219,8 +219,9 @@ def gpu_arm(args):
         # device-to-host copy of one step runs beside the next step's kernels (the last copy is waited for before the clock
         # stops, see `timed`)
         ids = ids_host.to(dev, non_blocking=True)
-        mask = mask_host.to(dev, non_blocking=True)
-        out = model(input_ids=ids, attention_mask=mask).last_hidden_state
+        # the mask is handed over where it is, in pinned host memory: the model reads the lengths there and copies it to
+        # the device itself (the bytes are counted in h2d_bytes_per_step)
+        out = model(input_ids=ids, attention_mask=mask_host).last_hidden_state
         done = torch.cuda.Event()
         done.record()
         with torch.cuda.stream(copy_stream):

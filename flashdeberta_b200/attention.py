@@ -33,10 +33,11 @@ class PackedSequences:
         self.batch, self.seqlen = int(batch), int(seqlen)
 
     @classmethod
-    def from_mask(cls, mask2d: torch.Tensor) -> Optional["PackedSequences"]:
+    def from_mask(cls, mask2d: torch.Tensor, device=None) -> Optional["PackedSequences"]:
         """None when the batch has no padding.  One host read (total tokens and longest sequence) per model forward; the
         reference does one per sequence per layer (src/flashdeberta/ops/flash_attention_varlen.py:71-83) plus one per
-        layer (padding.py:82)."""
+        layer (padding.py:82).  With a mask on the host the read waits for nothing; ``device`` is then where the index
+        tensors go."""
         m = mask2d != 0
         lens = m.sum(dim=-1, dtype=torch.int32)
         if lens.numel() == 0:
@@ -47,6 +48,8 @@ class PackedSequences:
         cu = torch.zeros(lens.numel() + 1, dtype=torch.int32, device=mask2d.device)
         cu[1:] = torch.cumsum(lens, 0)
         indices = torch.nonzero(m.flatten(), as_tuple=False).flatten()
+        if device is not None and cu.device != torch.device(device):
+            cu, indices = cu.to(device, non_blocking=True), indices.to(device, non_blocking=True)
         return cls(cu, max_len, indices, mask2d.shape[0], mask2d.shape[1])
 
     def pack(self, x: torch.Tensor) -> torch.Tensor:

@@ -147,7 +147,8 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         return self._rel_cache[1]
 
     def forward(self, hidden_states, attention_mask, output_hidden_states=True, output_attentions=False,
-                query_states=None, relative_pos=None, return_dict=True):
+                query_states=None, relative_pos=None, return_dict=True, host_mask=None):
+        """``host_mask``: the same mask as a host tensor, when the caller still has it there (see the model's forward)."""
         if not self._fused:
             return super().forward(hidden_states, attention_mask, output_hidden_states, output_attentions,
                                    query_states, relative_pos, return_dict)
@@ -155,7 +156,15 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         # tensor, unmodified, coming back (a serving loop with a resident mask) costs no kernels and no host read.
         key = (attention_mask.data_ptr(), attention_mask._version, tuple(attention_mask.shape), attention_mask.dtype)
         cached = self._mask_cache
-        if cached is not None and cached[0] == key and cached[1] is attention_mask:
+        if host_mask is not None:
+            dev = hidden_states.device if torch.is_tensor(hidden_states) else attention_mask.device
+            input_mask = attention_mask if attention_mask.dim() <= 2 else attention_mask.sum(-2) > 0
+            seq_lens = lengths_from_mask(host_mask).to(dev, non_blocking=True)
+            packed_all, looked = None, False
+            if getattr(self.config_pack, "pack_sequences", True) and self.conv is None and input_mask.dim() == 2:
+                host2d = host_mask if host_mask.dim() <= 2 else host_mask.sum(-2) > 0
+                packed_all, looked = PackedSequences.from_mask(host2d, device=dev), True
+        elif cached is not None and cached[0] == key and cached[1] is attention_mask:
             input_mask, seq_lens, packed_all, looked = cached[2]
         else:
             if attention_mask.dim() <= 2:
@@ -251,14 +260,20 @@ class FlashDebertaV2Model(DebertaV2Model):
             input_shape, device = inputs_embeds.size()[:-1], inputs_embeds.device
         else:
             raise ValueError("You have to specify either input_ids or inputs_embeds")
+        host_mask = None
         if attention_mask is None:
             attention_mask = torch.ones(input_shape, device=device)
+        elif attention_mask.device.type == "cpu" and device.type == "cuda":
+            # A mask that is still on the host is analysed there (lengths, padded or not: a few microseconds of host work
+            # and no wait for the device); the device only gets the copy the embeddings multiply by.
+            host_mask = attention_mask
+            attention_mask = attention_mask.to(device, non_blocking=True)
         if token_type_ids is None:
             token_type_ids = torch.zeros(input_shape, dtype=torch.long, device=device)
         embedding_output = self.embeddings(input_ids=input_ids, token_type_ids=token_type_ids,
                                            position_ids=position_ids, mask=attention_mask, inputs_embeds=inputs_embeds)
         enc = self.encoder(embedding_output, attention_mask, output_hidden_states=bool(output_hidden_states),
-                           output_attentions=False, return_dict=True)
+                           output_attentions=False, return_dict=True, host_mask=host_mask)
         if not return_dict:
             return (enc.last_hidden_state,) + ((enc.hidden_states,) if output_hidden_states else ())
         return BaseModelOutput(last_hidden_state=enc.last_hidden_state,

@@ -816,6 +816,10 @@ def test_model_repeated_calls_and_mask_changes():
     assert torch.equal(run(ids, mask), padded)
     mask[1, 120:] = 1                                  # and back
     assert torch.equal(run(ids, mask), first)
+    host = torch.ones(B, L)                            # a mask still on the host: analysed there, same results
+    assert torch.equal(run(ids, host), first)
+    host[1, 120:] = 0
+    assert torch.equal(run(ids, host.pin_memory()), padded)
     ids3 = torch.randint(1, 500, (2, 200), device=DEV)  # another shape
     mask3 = torch.ones(2, 200, device=DEV)
     assert torch.equal(run(ids3, mask3), fresh(ids3, mask3))
