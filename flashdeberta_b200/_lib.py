@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libfdb_b200.so")
 
 FDB_OK = 0
 FDB_BF16, FDB_FP32, FDB_E4M3 = 0, 1, 2
-FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN = 1, 2
+FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN, FDB_DEV_BAD_INDEX = 1, 2, 4
 STATIC_SCRATCH_BYTES = 8 << 20
 ABI_VERSION = 2
 PREPARED_SCHEDULE, PREPARED_TABLES = 1, 2  # fdb_attn_params.prepared
@@ -47,7 +47,7 @@ class AttnParams(C.Structure):
 EXPORTS = (
     "fdb_abi_version", "fdb_last_error", "fdb_status_string", "fdb_build_bucket_lut", "fdb_relative_index",
     "fdb_attn_workspace_bytes", "fdb_attn_fwd", "fdb_attn_fwd_static", "fdb_attn_fwd_check", "fdb_relative_index_matrix",
-    "fdb_quantize_e4m3", "fdb_add_layernorm", "fdb_linear_gelu",
+    "fdb_quantize_e4m3", "fdb_add_layernorm", "fdb_linear_gelu", "fdb_embed_layernorm",
 )
 
 _lib = None
@@ -95,6 +95,9 @@ def load() -> C.CDLL:
     lib.fdb_add_layernorm.restype = C.c_int
     lib.fdb_add_layernorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                       C.c_float, C.c_void_p]
+    lib.fdb_embed_layernorm.restype = C.c_int
+    lib.fdb_embed_layernorm.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_int64, C.c_int32, C.c_float, C.c_void_p, C.c_void_p]
     lib.fdb_linear_gelu.restype = C.c_int
     lib.fdb_linear_gelu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                     C.c_void_p, C.c_void_p]

@@ -24,6 +24,7 @@ from transformers.modeling_outputs import BaseModelOutput
 from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
 from transformers.models.deberta_v2.modeling_deberta_v2 import (
     DebertaV2Attention,
+    DebertaV2Embeddings,
     DebertaV2Encoder,
     DebertaV2ForMaskedLM,
     DebertaV2ForMultipleChoice,
@@ -88,6 +89,24 @@ class FlashDebertaV2Output(DebertaV2Output):
 
     def forward(self, hidden_states, input_tensor):
         return _dense_add_layernorm(self, hidden_states, input_tensor)
+
+
+class FlashDebertaV2Embeddings(DebertaV2Embeddings):
+    """Same parameters as transformers' module (the reference keeps it inside FlashDebertaV2Model,
+    src/flashdeberta/model.py:394-428).  When the input is word embeddings alone (no position term, no token types, no
+    projection: the DeBERTa-v3 configuration) and the case allows it (inference, CUDA, bf16), gather, LayerNorm and the
+    multiplication by the mask are one kernel."""
+
+    def forward(self, input_ids=None, token_type_ids=None, position_ids=None, mask=None, inputs_embeds=None):
+        ln, table = self.LayerNorm, self.word_embeddings.weight
+        if (input_ids is not None and inputs_embeds is None and self.position_embeddings is None
+                and not self.position_biased_input and self.token_type_embeddings is None and self.embed_proj is None
+                and not self.training and not torch.is_grad_enabled() and table.is_cuda and input_ids.is_cuda
+                and ops.can_fuse_add_layernorm(table, ln.weight, ln.bias)
+                and (mask is None or mask.numel() == input_ids.numel())):
+            return ops.embed_layernorm(input_ids, table, ln.weight, ln.bias, ln.eps, row_scale=mask)
+        return super().forward(input_ids=input_ids, token_type_ids=token_type_ids, position_ids=position_ids, mask=mask,
+                               inputs_embeds=inputs_embeds)
 
 
 class FlashDebertaV2Intermediate(DebertaV2Intermediate):
@@ -232,6 +251,8 @@ class FlashDebertaV2Model(DebertaV2Model):
     def __init__(self, config):
         super().__init__(config)
         self.encoder = FlashDebertaV2Encoder(config)
+        if self.encoder._fused:
+            self.embeddings = FlashDebertaV2Embeddings(config)
         self.post_init()
 
     def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,

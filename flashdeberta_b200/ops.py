@@ -18,7 +18,7 @@ import torch
 from . import _lib, bucket
 
 __all__ = [
-    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3", "add_layernorm", "can_fuse_add_layernorm", "linear_gelu", "can_fuse_linear_gelu",
+    "disentangled_attention", "disentangled_attention_fp8", "disentangled_attention_static", "disentangled_attention_check", "relative_index_matrix", "quantize_e4m3", "add_layernorm", "can_fuse_add_layernorm", "linear_gelu", "can_fuse_linear_gelu", "embed_layernorm",
     "check_status", "launch_count", "PreparedWorkspace",
 ]
 
@@ -51,6 +51,8 @@ def check_status(device=None) -> None:
                 what.append("a bounded wait inside the attention kernel ran out (output invalid)")
             if v & _lib.FDB_DEV_BAD_SEQLEN:
                 what.append("cu_seqlens/seq_lens hold a length below zero or above max_seqlen")
+            if v & _lib.FDB_DEV_BAD_INDEX:
+                what.append("an input id lies outside the embedding table")
             raise RuntimeError("flashdeberta_b200 device status %d: %s" % (v, "; ".join(what)))
 
 
@@ -401,6 +403,38 @@ def add_layernorm(x: torch.Tensor, residual: Optional[torch.Tensor], weight: tor
                                          x2.shape[0], hidden, float(eps), C.c_void_p(stream)))
         _launches += 1
     return out.view(x.shape)
+
+
+def embed_layernorm(ids: torch.Tensor, table: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                    row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm(table[ids]) * row_scale[..., None] in one kernel (``fdb_embed_layernorm``): transformers'
+    DebertaV2Embeddings for word embeddings alone, which the reference's model keeps (src/flashdeberta/model.py:394-428).
+    ids: integer tensor of any shape; table: (vocab, hidden) bf16; row_scale: ids' shape (the mask) or None.  Returns
+    bf16 of shape ids.shape + (hidden,)."""
+    global _launches
+    hidden = table.shape[-1]
+    if not (table.is_cuda and table.dim() == 2 and table.is_contiguous() and can_fuse_add_layernorm(table, weight, bias)):
+        raise ValueError("embed_layernorm needs a contiguous CUDA bf16 table with hidden a multiple of 256 up to 2048")
+    lib = _lib.load()
+    ids1 = ids.reshape(-1).to(device=table.device, dtype=torch.int64).contiguous()
+    scale1 = None
+    if row_scale is not None:
+        if row_scale.numel() != ids1.numel():
+            raise ValueError("row_scale must have one entry per id")
+        # the mask as the eager expression uses it: cast to the activation dtype first
+        scale1 = row_scale.reshape(-1).to(device=table.device, dtype=torch.bfloat16).to(torch.float32).contiguous()
+    out = torch.empty(ids1.numel(), hidden, dtype=torch.bfloat16, device=table.device)
+    if ids1.numel() == 0:
+        return out.view(*ids.shape, hidden)
+    with torch.cuda.device(table.device):
+        stream = torch.cuda.current_stream(table.device).cuda_stream
+        _lib.check(lib.fdb_embed_layernorm(ids1.data_ptr(), table.data_ptr(), table.shape[0],
+                                           weight.contiguous().data_ptr(), bias.contiguous().data_ptr(),
+                                           scale1.data_ptr() if scale1 is not None else None, out.data_ptr(),
+                                           ids1.numel(), hidden, float(eps), _status_word(table.device).data_ptr(),
+                                           C.c_void_p(stream)))
+        _launches += 1
+    return out.view(*ids.shape, hidden)
 
 
 def can_fuse_linear_gelu(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> bool:

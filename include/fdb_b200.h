@@ -48,6 +48,7 @@ typedef enum fdb_dtype {
 /* Bits of the device status word written by kernels (0 = no anomaly). */
 #define FDB_DEV_TIMEOUT 1u      /* a bounded wait inside a kernel ran out; the output is invalid */
 #define FDB_DEV_BAD_SEQLEN 2u   /* cu_seqlens not monotone / a length below zero or above max_seqlen */
+#define FDB_DEV_BAD_INDEX 4u    /* fdb_embed_layernorm met an id outside the table (the row was taken from its edge) */
 
 /*
  * One attention call.  Replaces, in one launch sequence, what the reference does in
@@ -226,6 +227,20 @@ FDB_API int fdb_quantize_e4m3(const void* x_bf16, int64_t row_stride, int64_t he
  */
 FDB_API int fdb_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                               int64_t rows, int32_t hidden, float eps, void* stream);
+
+/*
+ * out[r] = LayerNorm(table[ids[r]]) * row_scale[r]: the embedding stage of the model when the input is word embeddings
+ * alone (DeBERTa-v3: position_biased_input off, no token types, no projection).  The reference inherits the stage from
+ * transformers (DebertaV2Embeddings inside FlashDebertaV2Model, src/flashdeberta/model.py:394-428): an embedding gather, a
+ * zero tensor for the absent position term, a layer norm and a multiplication by the mask — four kernels and seven passes
+ * over the (rows, hidden) activation, here one kernel and two.  ids: device int64, rows entries; table: (table_rows,
+ * hidden) bf16 contiguous; row_scale: device fp32, rows entries, or NULL; the normalised value is rounded to bf16 before
+ * it is scaled.  hidden a multiple of 256 up to 2048.  An id outside [0, table_rows) sets FDB_DEV_BAD_INDEX in *status
+ * (may be NULL) and reads the nearest edge of the table.
+ */
+FDB_API int fdb_embed_layernorm(const int64_t* ids, const void* table, int64_t table_rows, const void* gamma,
+                                const void* beta, const float* row_scale, void* out, int64_t rows, int32_t hidden,
+                                float eps, int32_t* status, void* stream);
 
 /*
  * out = GELU(x . weight^T + bias), erf form, bf16 in and out, fp32 accumulation in tensor memory; the sum is rounded to bf16

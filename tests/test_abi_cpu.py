@@ -196,3 +196,37 @@ def test_linear_gelu_argument_errors(x, weight, k, n, code):
 def test_linear_gelu_zero_rows_is_a_no_op():
     lib = _lib.load()
     assert lib.fdb_linear_gelu(0x1000, 0x1000, None, 0x2000, 0, 768, 3072, None, None) == 0
+
+
+@pytest.mark.parametrize("ids,table,rows_in_table,hidden,code", [
+    (0, 0x1000, 100, 768, -1),         # ids NULL
+    (0x1000, 0, 100, 768, -1),         # table NULL
+    (0x1000, 0x1000, 0, 768, -1),      # empty table
+    (0x1000, 0x1000, 100, 100, -2),    # hidden not a multiple of 256
+    (0x1000, 0x1008, 100, 768, -3),    # table not 16-byte aligned
+])
+def test_embed_layernorm_argument_errors(ids, table, rows_in_table, hidden, code):
+    lib = _lib.load()
+    rc = lib.fdb_embed_layernorm(ids or None, table or None, rows_in_table, 0x1000, 0x1000, None, 0x2000, 4, hidden, 1e-7,
+                                 None, None)
+    assert rc == code
+    assert lib.fdb_last_error().decode() != ""
+
+
+def test_model_keeps_transformers_parameter_names():
+    """Every block this package swaps in (embeddings, attention, intermediate and output blocks) keeps transformers'
+    state-dict keys, so checkpoints load unchanged; on CPU tensors the blocks run transformers' own code."""
+    from transformers.models.deberta_v2.configuration_deberta_v2 import DebertaV2Config
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DebertaV2Model
+    from flashdeberta_b200 import FlashDebertaV2Model
+    cfg = DebertaV2Config(hidden_size=256, num_attention_heads=4, intermediate_size=512, num_hidden_layers=2,
+                          relative_attention=True, position_buckets=32, max_relative_positions=64,
+                          pos_att_type="c2p|p2c", share_att_key=True, vocab_size=100, type_vocab_size=0,
+                          position_biased_input=False, norm_rel_ebd="layer_norm")
+    cfg.attn_backend = "b200"
+    ours, theirs = FlashDebertaV2Model(cfg).eval(), DebertaV2Model(cfg).eval()
+    assert set(ours.state_dict().keys()) == set(theirs.state_dict().keys())
+    theirs.load_state_dict(ours.state_dict())
+    ids, mask = torch.randint(1, 100, (2, 9)), torch.ones(2, 9)
+    with torch.no_grad():
+        assert torch.equal(ours.embeddings(input_ids=ids, mask=mask), theirs.embeddings(input_ids=ids, mask=mask))

@@ -731,6 +731,47 @@ def test_quantize_e4m3_scales_and_values(lens, heads, strided):
         at += n
 
 
+@pytest.mark.parametrize("shape,hidden,vocab,masked", [((8, 2048), 768, 5000, True), ((3, 77), 1024, 300, True),
+                                                        ((5,), 256, 10, False)])
+def test_embed_layernorm_vs_torch(shape, hidden, vocab, masked):
+    """fdb_embed_layernorm against torch's embedding -> layer_norm -> mask multiplication in bf16 (same fp32 statistics
+    and rounding points: at most one bf16 ulp apart, equal almost everywhere) and against the fp32 expression."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(hidden + vocab)
+    table = torch.randn(vocab, hidden, generator=g).bfloat16().to(DEV)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).bfloat16().to(DEV)
+    b = (0.1 * torch.randn(hidden, generator=g)).bfloat16().to(DEV)
+    ids = torch.randint(0, vocab, shape, generator=g).to(DEV)
+    mask = (torch.rand(shape, generator=g) > 0.3).long().to(DEV) if masked else None
+    out = ops.embed_layernorm(ids, table, w, b, 1e-7, row_scale=mask)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert out.shape == (*shape, hidden) and out.dtype == torch.bfloat16
+    F = torch.nn.functional
+    ref = F.layer_norm(F.embedding(ids, table), (hidden,), w, b, 1e-7)
+    want32 = F.layer_norm(F.embedding(ids, table).float(), (hidden,), w.float(), b.float(), 1e-7)
+    if masked:
+        ref = ref * mask.unsqueeze(-1).to(ref.dtype)
+        want32 = want32 * mask.unsqueeze(-1)
+        assert torch.count_nonzero(out[mask == 0]) == 0
+    diff = (out.float() - ref.float()).abs()
+    assert diff.max().item() <= 6.3e-2 and (diff > 0).float().mean().item() < 0.1
+    err = (out.float() - want32).abs()
+    assert err.max().item() <= 4e-2 and err.mean().item() <= 3e-3
+
+
+def test_embed_layernorm_reports_an_id_outside_the_table():
+    ops = _ops()
+    table = torch.randn(10, 256).bfloat16().to(DEV)
+    w = torch.ones(256, dtype=torch.bfloat16, device=DEV)
+    ids = torch.tensor([1, 10, 3], device=DEV)
+    out = ops.embed_layernorm(ids, table, w, torch.zeros_like(w), 1e-7)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    with pytest.raises(RuntimeError, match="embedding table"):
+        ops.check_status()
+
+
 def test_call_can_be_captured_in_a_cuda_graph_and_replayed():
     """No host synchronisation, no allocation inside the library: a call (set-up kernels + fused kernel) is capturable;
     the replay on new inputs matches a direct call bit for bit."""
