@@ -21,19 +21,36 @@ namespace {
 constexpr int kQuantThreads = 256;
 constexpr int kChunkRows = 64;
 
-// (row, head) pairs of rows [r0 + chunk * 64, ...) of the slab, eight lanes (16 bytes each) per pair
+constexpr int kUnroll = 4;  // 16-byte loads in flight per thread
+
+// Walks the (row, head) pairs of this CTA's 64-row chunks of its slab, eight lanes (16 bytes each) per pair and kUnroll
+// pairs per thread at a time: first all loads, then `body(live, r, h, sub, v)` for each.
 template <typename F>
-__device__ __forceinline__ void walk_slab(const int32_t* __restrict__ slab_start, int heads, F&& body) {
+__device__ __forceinline__ void walk_slab(const __nv_bfloat16* __restrict__ x, int64_t row_stride, int64_t head_stride,
+                                          const int32_t* __restrict__ slab_start, int heads, F&& body) {
   const int slab = blockIdx.y;
   const int r0 = slab_start[slab], len = max(slab_start[slab + 1] - r0, 0);
   const int sub = threadIdx.x & 7;
+  constexpr int kStep = kQuantThreads >> 3;  // pairs per pass of the CTA
   for (int chunk = blockIdx.x; chunk * kChunkRows < len; chunk += gridDim.x) {
     const int rows = min(kChunkRows, len - chunk * kChunkRows);
     const int pairs = rows * heads;
-    for (int p = threadIdx.x >> 3; p < ((pairs + 31) & ~31); p += kQuantThreads >> 3) {  // whole warps stay together
-      const bool live = p < pairs;
-      const int r = r0 + chunk * kChunkRows + (live ? p / heads : 0), h = live ? p % heads : 0;
-      body(live, r, h, sub);
+    const int first_row = r0 + chunk * kChunkRows;
+    for (int p0 = threadIdx.x >> 3; (p0 & ~3) < pairs; p0 += kStep * kUnroll) {  // a warp's four pairs stay together
+      uint4 v[kUnroll];
+      int r[kUnroll], h[kUnroll];
+      bool live[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int p = p0 + u * kStep;
+        live[u] = p < pairs;
+        r[u] = first_row + (live[u] ? p / heads : 0);
+        h[u] = live[u] ? p % heads : 0;
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (live[u]) v[u] = *reinterpret_cast<const uint4*>(x + r[u] * row_stride + h[u] * head_stride + sub * 8);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) body(live[u], r[u], h[u], sub, v[u]);
     }
   }
 }
@@ -44,16 +61,14 @@ __global__ void __launch_bounds__(kQuantThreads) amax_kernel(const __nv_bfloat16
   extern __shared__ unsigned int s_amax[];
   for (int h = threadIdx.x; h < heads; h += kQuantThreads) s_amax[h] = 0u;
   __syncthreads();
-  walk_slab(slab_start, heads, [&](bool live, int r, int h, int sub) {
+  walk_slab(x, row_stride, head_stride, slab_start, heads, [&](bool live, int, int h, int sub, const uint4& v) {
+    // whole warps get here; a dead pair holds zeros
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
     float a = 0.f;
-    if (live) {
-      const uint4 v = *reinterpret_cast<const uint4*>(x + r * row_stride + h * head_stride + sub * 8);
-      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(b[k]);
-        a = fmaxf(a, fmaxf(fabsf(f.x), fabsf(f.y)));
-      }
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(b[k]);
+      a = fmaxf(a, fmaxf(fabsf(f.x), fabsf(f.y)));
     }
     a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
     a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
@@ -71,10 +86,9 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_kernel(const __nv_bflo
                                                                  int64_t head_stride, const int32_t* __restrict__ slab_start,
                                                                  int heads, uint8_t* __restrict__ y,
                                                                  const unsigned int* __restrict__ amax_bits) {
-  walk_slab(slab_start, heads, [&](bool live, int r, int h, int sub) {
+  walk_slab(x, row_stride, head_stride, slab_start, heads, [&](bool live, int r, int h, int sub, const uint4& v) {
     if (!live) return;
     const float inv = 1.f / scale_of(amax_bits[(int64_t)blockIdx.y * heads + h]);
-    const uint4 v = *reinterpret_cast<const uint4*>(x + r * row_stride + h * head_stride + sub * 8);
     const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
     uint16_t o[4];
 #pragma unroll
