@@ -12,10 +12,11 @@ LIB_PATH = os.path.join(_PKG_DIR, "libfdb_b200.so")
 
 FDB_OK = 0
 FDB_BF16, FDB_FP32, FDB_E4M3 = 0, 1, 2
-FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN, FDB_DEV_BAD_INDEX = 1, 2, 4
+FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN, FDB_DEV_BAD_INDEX, FDB_DEV_BAD_MASK = 1, 2, 4, 8
 STATIC_SCRATCH_BYTES = 8 << 20
-ABI_VERSION = 2
+ABI_VERSION = 3
 PREPARED_SCHEDULE, PREPARED_TABLES = 1, 2  # fdb_attn_params.prepared
+TUNE_ONE_LAUNCH, TUNE_TWO_LAUNCHES, TUNE_FAR_ONE_TEAM, TUNE_FAR_TWO_TEAMS = 1, 2, 4, 8  # fdb_attn_params.tune
 
 
 class AttnParams(C.Structure):
@@ -40,7 +41,7 @@ class AttnParams(C.Structure):
         ("lse", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
         ("status", C.c_void_p),
-        ("prepared", C.c_uint32),
+        ("prepared", C.c_uint32), ("tune", C.c_uint32),
     ]
 
 
@@ -90,7 +91,7 @@ def load() -> C.CDLL:
     lib.fdb_relative_index_matrix.restype = C.c_int
     lib.fdb_relative_index_matrix.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.fdb_quantize_e4m3.restype = C.c_int
-    lib.fdb_quantize_e4m3.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+    lib.fdb_quantize_e4m3.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                       C.c_void_p, C.c_void_p, C.c_void_p]
     lib.fdb_add_layernorm.restype = C.c_int
     lib.fdb_add_layernorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,

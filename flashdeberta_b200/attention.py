@@ -19,7 +19,7 @@ from typing import Optional
 import torch
 from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfAttention
 
-from . import ops
+from . import _lib, ops
 
 
 class PackedSequences:
@@ -63,21 +63,38 @@ class PackedSequences:
         return out.view(self.batch, self.seqlen, *x.shape[2:])
 
 
-def lengths_from_mask(attention_mask: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+def lengths_from_mask(attention_mask: Optional[torch.Tensor], check: bool = True) -> Optional[torch.Tensor]:
     """Per-sequence valid lengths (int32, on the mask's device) from any of the mask forms the module is handed.
-    Returns None for "everything valid".  No host synchronisation."""
+    Returns None for "everything valid".  No host synchronisation.
+
+    The dense kernel path addresses a sequence by its length alone, so the valid tokens must be a prefix of each row
+    (right padding).  The reference un-pads through the mask's indices and takes any layout
+    (src/flashdeberta/padding.py:113-166); here other layouts go through ``PackedSequences`` (what the encoder does for any
+    padded batch), and a mask that is not a prefix is refused: a ValueError for a mask on the host, the FDB_DEV_BAD_MASK bit
+    of the device status word (raised by ``ops.check_status``) for a mask on the device."""
     if attention_mask is None:
         return None
     m = attention_mask
     if m.dim() == 1:  # already lengths
         return m.to(torch.int32)
-    if m.dim() == 4:  # (B, 1, L, L): row of the first token
-        m = m[:, 0, 0, :]
+    if m.dim() == 4:  # (B, 1, L, L), entry (i, j) = valid_i * valid_j: the diagonal says which tokens are valid
+        m = torch.diagonal(m[:, 0], dim1=-2, dim2=-1)
     elif m.dim() == 3:  # (B, L, L)
-        m = m[:, 0, :]
+        m = torch.diagonal(m, dim1=-2, dim2=-1)
     elif m.dim() != 2:
         raise ValueError(f"attention_mask with {attention_mask.dim()} dims is not supported")
-    return (m != 0).sum(dim=-1, dtype=torch.int32)
+    valid = m != 0
+    lens = valid.sum(dim=-1, dtype=torch.int32)
+    if check and not torch.compiler.is_compiling():
+        prefix = torch.arange(m.shape[-1], device=m.device)[None, :] < lens[:, None]
+        bad = (valid != prefix).any()
+        if m.device.type == "cpu":
+            if bool(bad):
+                raise ValueError("attention_mask is not right-padded: the valid tokens of every row must come first "
+                                 "(pack the batch, e.g. through FlashDebertaV2Model, to use other layouts)")
+        else:
+            ops.flag_status(m.device, bad, _lib.FDB_DEV_BAD_MASK)
+    return lens
 
 
 class FlashDisentangledSelfAttention(DisentangledSelfAttention):
@@ -107,8 +124,9 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
             wk, wq = getattr(self, "pos_key_proj", None), getattr(self, "pos_query_proj", None)
         key = None
         if not self.training and not torch.is_grad_enabled():
-            key = (id(rel_embeddings), rel_embeddings._version, rel_embeddings.device, dtype,
-                   tuple((p.data_ptr(), p._version) for m in (wk, wq) if m is not None for p in m.parameters()))
+            # the table is kept alive below, so its identity stays its own
+            key = (id(rel_embeddings), ops.tensor_stamp(rel_embeddings, held=True), rel_embeddings.device, dtype,
+                   tuple(ops.tensor_stamp(p, held=True) for m in (wk, wq) if m is not None for p in m.parameters()))
             if self._pos_cache is not None and self._pos_cache[0] == key:
                 return self._pos_cache[1], self._pos_cache[2]
         span2 = 2 * self.pos_ebd_size

@@ -43,6 +43,10 @@ int validate(const fdb_attn_params* p, bool fused) {
   if (!(p->sm_scale > 0.f)) return fail(FDB_ERR_INVALID_ARGUMENT, "sm_scale must be positive");
   if ((p->prepared & ~(FDB_PREPARED_SCHEDULE | FDB_PREPARED_TABLES)) != 0)
     return fail(FDB_ERR_INVALID_ARGUMENT, "unknown bits in prepared: 0x%x", p->prepared);
+  if ((p->tune & ~(FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES | FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS)) != 0 ||
+      (p->tune & (FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES)) == (FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES) ||
+      (p->tune & (FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS)) == (FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS))
+    return fail(FDB_ERR_INVALID_ARGUMENT, "unknown or contradictory bits in tune: 0x%x", p->tune);
   if (p->pos_key != nullptr || p->pos_query != nullptr) {
     const int span = p->position_buckets > 0 ? p->position_buckets : p->max_relative_positions;
     if (span <= 0) return fail(FDB_ERR_INVALID_ARGUMENT, "position tables given but att_span is %d", span);
@@ -156,14 +160,19 @@ int fdb_relative_index_matrix(const int16_t* bucket_lut, int32_t lut_d_min, int3
   return launch_relative_index_matrix(bucket_lut, lut_d_min, lut_len, len_q, len_k, out, stream);
 }
 
-int fdb_quantize_e4m3(const void* x_bf16, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
-                      int32_t n_slabs, int32_t heads, int32_t head_dim, void* y_e4m3, float* scale, void* stream) {
+int fdb_quantize_e4m3(const void* x_bf16, int64_t rows, int64_t row_stride, int64_t head_stride,
+                      const int32_t* slab_start, int32_t n_slabs, int32_t heads, int32_t head_dim, void* y_e4m3,
+                      float* scale, void* stream) {
   clear_error();
   if (x_bf16 == nullptr || slab_start == nullptr || y_e4m3 == nullptr || scale == nullptr || n_slabs < 0 || heads <= 0 ||
-      head_dim <= 0 || head_dim % 8 != 0)
+      head_dim <= 0 || head_dim % 8 != 0 || rows < 0 || rows > 2147483647LL)
     return fail(FDB_ERR_INVALID_ARGUMENT, "quantize_e4m3: bad argument");
-  if (n_slabs == 0) return FDB_OK;
-  return launch_quantize_e4m3(x_bf16, row_stride, head_stride, slab_start, n_slabs, heads, head_dim, y_e4m3, scale, stream);
+  // the kernels load 16 bytes at x + row*row_stride + head*head_stride + 8*i and store 8 bytes into y
+  if (!aligned16(x_bf16) || (reinterpret_cast<uintptr_t>(y_e4m3) & 7u) != 0 || row_stride <= 0 || head_stride <= 0 ||
+      row_stride % 8 != 0 || head_stride % 8 != 0)
+    return fail(FDB_ERR_ALIGNMENT, "quantize_e4m3: x must be 16-byte aligned, y 8-byte aligned, strides positive multiples of 8 elements");
+  if (n_slabs == 0 || rows == 0) return FDB_OK;
+  return launch_quantize_e4m3(x_bf16, rows, row_stride, head_stride, slab_start, n_slabs, heads, head_dim, y_e4m3, scale, stream);
 }
 
 }  // extern "C"

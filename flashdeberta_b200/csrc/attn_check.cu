@@ -38,6 +38,7 @@ struct CheckArgs {
   int batch, max_seqlen, total_rows, heads, head_dim, table_rows;
   float sm_scale;
   float* lse;
+  int32_t* status;
 };
 
 template <typename T>
@@ -59,6 +60,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) attn_check_kernel(CheckAr
     }
     start = a.cu_seqlens[lo];
     len = a.cu_seqlens[lo + 1] - start;
+    // lengths the packed layout cannot hold are reported and cut to what exists, as the set-up kernel of the fused path does
+    if (len < 0 || len > a.max_seqlen || start < 0 || (int64_t)start + len > a.total_rows) {
+      if (lane == 0 && a.status != nullptr) atomicOr(reinterpret_cast<unsigned int*>(a.status), FDB_DEV_BAD_SEQLEN);
+      start = start < 0 ? 0 : (start > a.total_rows ? a.total_rows : start);
+      len = len < 0 ? 0 : (len > a.max_seqlen ? a.max_seqlen : len);
+      if (len > a.total_rows - start) len = a.total_rows - start;
+    }
     if (row < start || row >= start + len) len = 0;  // row past the last sequence, or an empty one
   } else {
     const int b = row / a.max_seqlen;
@@ -157,7 +165,8 @@ int launch_attn_check(const fdb_attn_params& p, void* stream) {
   a.batch = p.batch; a.max_seqlen = p.max_seqlen; a.total_rows = p.total_rows; a.heads = p.heads;
   a.head_dim = p.head_dim;
   a.table_rows = 2 * (p.position_buckets > 0 ? p.position_buckets : p.max_relative_positions);
-  a.sm_scale = p.sm_scale; a.lse = p.lse;
+  a.sm_scale = p.sm_scale; a.lse = p.lse; a.status = p.status;
+  if (p.heads > 65535) return fail(FDB_ERR_LIMIT, "the check kernel takes up to 65535 heads, got %d", p.heads);
   dim3 grid((p.total_rows + kWarpsPerBlock - 1) / kWarpsPerBlock, p.heads);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p.dtype == FDB_FP32) attn_check_kernel<float><<<grid, kWarpsPerBlock * 32, 0, s>>>(a);

@@ -40,9 +40,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include <cstdlib>
-#include <cstring>
-
 #include "internal.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.cuh"
@@ -739,15 +736,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 
 }  // namespace
 
-static bool use_far_for_plain() {
-  const char* env = std::getenv("FDB_ATTN_SPLIT");
-  return !(env != nullptr && env[0] == '0');
-}
-
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream) {
   const bool f8 = p.dtype == FDB_E4M3;
-  const char* which = std::getenv("FDB_ATTN_KERNEL");
-  if (!f8 && which != nullptr && std::strcmp(which, "serial") == 0) return launch_attn_fwd_serial(p, g, w, stream);
   FwdArgs a;
   char* ws = static_cast<char*>(p.workspace);
   int rc;
@@ -789,12 +779,12 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   // bf16: key tiles with saturated (or no) position terms go to the two-team kernel; with position terms the band tiles
   // follow in attn_fwd_kernel, which picks up the partial result on the same stream.
   const bool no_pos = a.xk == nullptr && a.xq == nullptr;
-  if (!f8 && (w.split || (no_pos && use_far_for_plain()))) {
+  if (!f8 && (w.split || (no_pos && !(p.tune & FDB_TUNE_ONE_LAUNCH)))) {
     // Two forms of the far kernel: one team per CTA and two CTAs per SM (the start and the end of a CTA overlap the other
     // CTA's work: better up to about 8192 keys), or two teams in one CTA with three K/V stages (better beyond).
-    // FDB_ATTN_FAR=1|2 forces one of them.
-    const char* far = std::getenv("FDB_ATTN_FAR");
-    const bool one_team = far != nullptr && (far[0] == '1' || far[0] == '2') ? far[0] == '1' : p.max_seqlen <= 8192;
+    // fdb_attn_params.tune can force one of them.
+    const bool one_team = (p.tune & (FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS)) ? (p.tune & FDB_TUNE_FAR_ONE_TEAM) != 0
+                                                                                        : p.max_seqlen <= 8192;
     rc = one_team ? launch_attn_fwd_far1(&a, slots, p.heads, stream) : launch_attn_fwd_far(&a, slots, p.heads, stream);
     if (rc != FDB_OK) return rc;
     if (no_pos) return FDB_OK;

@@ -67,6 +67,7 @@ extern "C" FDB_API int fdb_attn_fwd_static(const fdb_attn_params* p, void* strea
   q.workspace = scratch;
   q.workspace_bytes = kScratchBytes;
   q.prepared = 0;  // the scratch is shared by every call on this device
+  q.tune = (p->tune & ~FDB_TUNE_TWO_LAUNCHES) | FDB_TUNE_ONE_LAUNCH;  // one launch: no partial-result buffers
   // Nothing in the scratch has to start at zero: seq_info_kernel and expand_tables_kernel write every entry the fused
   // kernel reads, on this stream, before it runs.
   if ((rc = launch_prepare(q, g, w, stream)) != FDB_OK) return rc;

@@ -10,8 +10,6 @@
 //                      of rows and the fused kernel never evaluates the bucket function.
 #include <cuda_runtime.h>
 
-#include <cstdlib>
-
 #include "internal.h"
 
 namespace fdb {
@@ -32,9 +30,8 @@ static inline uint64_t align256(uint64_t x) { return (x + 255) & ~uint64_t(255);
 // Two launches pay off once a query tile has key tiles with saturated position terms on both sides of the band.
 static bool want_split(const fdb_attn_params& p) {
   if (p.dtype == FDB_E4M3 || (p.pos_key == nullptr && p.pos_query == nullptr)) return false;
-  const char* env = std::getenv("FDB_ATTN_SPLIT");
-  if (env != nullptr && env[0] == '0') return false;
-  if (env != nullptr && env[0] == '1') return true;
+  if (p.tune & FDB_TUNE_ONE_LAUNCH) return false;
+  if (p.tune & FDB_TUNE_TWO_LAUNCHES) return true;
   return p.max_seqlen >= 3584;
 }
 

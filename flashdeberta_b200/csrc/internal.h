@@ -59,12 +59,11 @@ int64_t tile_slots(const fdb_attn_params& p);
 int launch_attn_check(const fdb_attn_params& p, void* stream);
 int launch_prepare(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
-int launch_attn_fwd_serial(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
 int launch_attn_fwd_far(const void* fwd_args, int64_t slots, int heads, void* stream);  // fwd_args: fwd::FwdArgs
 int launch_attn_fwd_far1(const void* fwd_args, int64_t slots, int heads, void* stream);
 int launch_relative_index_matrix(const int16_t* lut, int32_t d_min, int32_t len, int32_t lq, int32_t lk, int32_t* out,
                                  void* stream);
-int launch_quantize_e4m3(const void* x, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
+int launch_quantize_e4m3(const void* x, int64_t rows, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
                          int32_t n_slabs, int32_t heads, int32_t head_dim, void* y, float* scale, void* stream);
 
 }  // namespace fdb

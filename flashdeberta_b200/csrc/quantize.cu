@@ -26,10 +26,12 @@ constexpr int kUnroll = 4;  // 16-byte loads in flight per thread
 // Walks the (row, head) pairs of this CTA's 64-row chunks of its slab, eight lanes (16 bytes each) per pair and kUnroll
 // pairs per thread at a time: first all loads, then `body(live, r, h, sub, v)` for each.
 template <typename F>
-__device__ __forceinline__ void walk_slab(const __nv_bfloat16* __restrict__ x, int64_t row_stride, int64_t head_stride,
-                                          const int32_t* __restrict__ slab_start, int heads, F&& body) {
+__device__ __forceinline__ void walk_slab(const __nv_bfloat16* __restrict__ x, int total_rows, int64_t row_stride,
+                                          int64_t head_stride, const int32_t* __restrict__ slab_start, int heads, F&& body) {
   const int slab = blockIdx.y;
-  const int r0 = slab_start[slab], len = max(slab_start[slab + 1] - r0, 0);
+  // slab bounds clamped to the rows that exist
+  const int r0 = min(max(slab_start[slab], 0), total_rows);
+  const int len = max(min(slab_start[slab + 1], total_rows) - r0, 0);
   const int sub = threadIdx.x & 7;
   constexpr int kStep = kQuantThreads >> 3;  // pairs per pass of the CTA
   for (int chunk = blockIdx.x; chunk * kChunkRows < len; chunk += gridDim.x) {
@@ -55,13 +57,14 @@ __device__ __forceinline__ void walk_slab(const __nv_bfloat16* __restrict__ x, i
   }
 }
 
-__global__ void __launch_bounds__(kQuantThreads) amax_kernel(const __nv_bfloat16* __restrict__ x, int64_t row_stride,
-                                                             int64_t head_stride, const int32_t* __restrict__ slab_start,
-                                                             int heads, unsigned int* __restrict__ amax_bits) {
+__global__ void __launch_bounds__(kQuantThreads) amax_kernel(const __nv_bfloat16* __restrict__ x, int total_rows,
+                                                             int64_t row_stride, int64_t head_stride,
+                                                             const int32_t* __restrict__ slab_start, int heads,
+                                                             unsigned int* __restrict__ amax_bits) {
   extern __shared__ unsigned int s_amax[];
   for (int h = threadIdx.x; h < heads; h += kQuantThreads) s_amax[h] = 0u;
   __syncthreads();
-  walk_slab(x, row_stride, head_stride, slab_start, heads, [&](bool live, int, int h, int sub, const uint4& v) {
+  walk_slab(x, total_rows, row_stride, head_stride, slab_start, heads, [&](bool live, int, int h, int sub, const uint4& v) {
     // whole warps get here; a dead pair holds zeros
     const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
     float a = 0.f;
@@ -82,11 +85,12 @@ __global__ void __launch_bounds__(kQuantThreads) amax_kernel(const __nv_bfloat16
 
 __device__ __forceinline__ float scale_of(unsigned int amax_bits) { return fmaxf(__uint_as_float(amax_bits), 1e-12f) / 448.f; }
 
-__global__ void __launch_bounds__(kQuantThreads) quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t row_stride,
-                                                                 int64_t head_stride, const int32_t* __restrict__ slab_start,
-                                                                 int heads, uint8_t* __restrict__ y,
+__global__ void __launch_bounds__(kQuantThreads) quantize_kernel(const __nv_bfloat16* __restrict__ x, int total_rows,
+                                                                 int64_t row_stride, int64_t head_stride,
+                                                                 const int32_t* __restrict__ slab_start, int heads,
+                                                                 uint8_t* __restrict__ y,
                                                                  const unsigned int* __restrict__ amax_bits) {
-  walk_slab(x, row_stride, head_stride, slab_start, heads, [&](bool live, int r, int h, int sub, const uint4& v) {
+  walk_slab(x, total_rows, row_stride, head_stride, slab_start, heads, [&](bool live, int r, int h, int sub, const uint4& v) {
     if (!live) return;
     const float inv = 1.f / scale_of(amax_bits[(int64_t)blockIdx.y * heads + h]);
     const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -110,7 +114,7 @@ __global__ void scale_kernel(float* __restrict__ scale, int n) {
 
 }  // namespace
 
-int launch_quantize_e4m3(const void* x, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
+int launch_quantize_e4m3(const void* x, int64_t rows, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
                          int32_t n_slabs, int32_t heads, int32_t head_dim, void* y, float* scale, void* stream) {
   if (head_dim != 64) return fail(FDB_ERR_UNSUPPORTED, "quantize_e4m3 is built for head_dim 64, got %d", head_dim);
   if (n_slabs <= 0 || heads <= 0) return FDB_OK;
@@ -124,8 +128,8 @@ int launch_quantize_e4m3(const void* x, int64_t row_stride, int64_t head_stride,
   const dim3 grid(per_slab, n_slabs);
   auto* xb = static_cast<const __nv_bfloat16*>(x);
   auto* bits = reinterpret_cast<unsigned int*>(scale);
-  amax_kernel<<<grid, kQuantThreads, sizeof(unsigned int) * heads, s>>>(xb, row_stride, head_stride, slab_start, heads, bits);
-  quantize_kernel<<<grid, kQuantThreads, 0, s>>>(xb, row_stride, head_stride, slab_start, heads, static_cast<uint8_t*>(y), bits);
+  amax_kernel<<<grid, kQuantThreads, sizeof(unsigned int) * heads, s>>>(xb, (int)rows, row_stride, head_stride, slab_start, heads, bits);
+  quantize_kernel<<<grid, kQuantThreads, 0, s>>>(xb, (int)rows, row_stride, head_stride, slab_start, heads, static_cast<uint8_t*>(y), bits);
   scale_kernel<<<(n + 255) / 256, 256, 0, s>>>(scale, n);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "quantize_e4m3 launch: %s", cudaGetErrorString(e));

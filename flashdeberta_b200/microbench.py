@@ -13,12 +13,22 @@ times the fused residual + LayerNorm kernel instead (algorithmic bytes: 3 * rows
     python -m flashdeberta_b200.microbench --linear-gelu --rows 16384 --hidden 768 --out-features 3072
 
 times the fused linear + GELU kernel (2 * rows * hidden * out_features FLOP) beside torch's linear followed by gelu.
+
+    python -m flashdeberta_b200.microbench --reference-triton --batch 8 --seq 2048
+
+times the reference's own attention path on the same GPU and the same q, k, v: the two bias GEMMs of
+src/flashdeberta/model.py:189-192 followed by flash_attention_with_disentangled (src/flashdeberta/ops/flash_attention.py:1088,
+Triton, compiled by the installed Triton), beside this library's fused call, and reports the largest difference between the
+two outputs.  Needs an unmodified copy of the reference package importable as ``flashdeberta`` (looked for under
+``baseline/_ref`` next to this package).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
+import sys
 
 import torch
 
@@ -81,6 +91,127 @@ def bench_linear_gelu(rows: int, k: int, n: int, iters: int, warmup: int, sets: 
                       "flops": flops, "l2": f"{sets} input buffers rotated; the output is allocated per call"}))
 
 
+def _time(fn, iters: int, warmup: int):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    times = []
+    for i in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times), min(times)
+
+
+def bench_reference_triton(B: int, L: int, H: int, iters: int, warmup: int, nsets: int):
+    """The reference's attention path (bias GEMMs + its Triton kernel) beside the fused call, same inputs."""
+    ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    try:
+        from flashdeberta.ops.flash_attention import flash_attention_with_disentangled
+    except Exception as e:  # the copy is not part of this repository's history
+        print(json.dumps({"op": "reference_triton", "unavailable": f"cannot import the reference package from {ref_root}: {e!r}"}))
+        return
+    import triton
+    dev = torch.device("cuda")
+    D = 64
+    g = torch.Generator(device="cpu").manual_seed(0)
+    sets = []
+    for _ in range(nsets):
+        q, k, v = (torch.randn(B, L, H, D, generator=g).bfloat16().to(dev) for _ in range(3))
+        # the reference's kernel wants (B, H, L, D) contiguous (its module makes these copies, model.py:137-140; they are
+        # left out of its time here)
+        sets.append((q, k, v, *(t.permute(0, 2, 1, 3).contiguous() for t in (q, k, v))))
+    pk, pq = (torch.randn(H, 512, D, generator=g).mul_(0.5).bfloat16().to(dev) for _ in range(2))
+    sm_scale = 1.0 / (3 * D) ** 0.5
+    kw = dict(max_seqlen=L, position_buckets=256, max_relative_positions=512)
+
+    def ours(i):
+        q, k, v = sets[i % nsets][:3]
+        return ops.disentangled_attention(q, k, v, pk, pq, **kw)
+
+    def theirs(i):
+        qt, kt, vt = sets[i % nsets][3:]
+        c2p = torch.matmul(qt, pk.unsqueeze(0).transpose(-1, -2))   # model.py:189-190
+        p2c = torch.matmul(kt, pq.unsqueeze(0).transpose(-1, -2))   # model.py:191-192
+        return flash_attention_with_disentangled(qt, kt, vt, c2p, p2c, False, sm_scale, 256, 512)
+
+    def theirs_kernel_only(i):
+        qt, kt, vt = sets[i % nsets][3:]
+        return flash_attention_with_disentangled(qt, kt, vt, bias[0], bias[1], False, sm_scale, 256, 512)
+
+    with torch.no_grad():
+        o_ours = ours(0)
+        o_ref = theirs(0).permute(0, 2, 1, 3)
+        diff = (o_ours.float() - o_ref.float()).abs()
+        qt, kt = sets[0][3], sets[0][4]
+        bias = (torch.matmul(qt, pk.unsqueeze(0).transpose(-1, -2)), torch.matmul(kt, pq.unsqueeze(0).transpose(-1, -2)))
+        ms_ours = _time(ours, iters, warmup)
+        ms_ref = _time(theirs, iters, warmup)
+        ms_ref_k = _time(theirs_kernel_only, iters, warmup)
+    ops.check_status()
+    f = attn_flops([L] * B, H)
+    print(json.dumps({
+        "op": "reference_triton", "batch": B, "seq": L, "heads": H, "triton": triton.__version__,
+        "fused_ms_median": ms_ours[0], "fused_tflops": f / ms_ours[0] / 1e9,
+        "reference_ms_median": ms_ref[0], "reference_tflops": f / ms_ref[0] / 1e9,
+        "reference_kernel_only_ms_median": ms_ref_k[0],
+        "speedup": ms_ref[0] / ms_ours[0],
+        "max_abs_diff_between_outputs": diff.max().item(), "mean_abs_diff_between_outputs": diff.mean().item(),
+        "note": "reference = bias GEMMs (model.py:189-192) + flash_attention_with_disentangled; its (B,H,L,D) copies are not timed"}))
+
+
+def bench_eager_gpu(B: int, L: int, H: int, iters: int, warmup: int):
+    """transformers' eager DisentangledSelfAttention module (the reference's fallback class, src/flashdeberta/model.py:255)
+    on the GPU in fp32 and bf16, beside this package's module with the same weights; whole module, projections included."""
+    from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfAttention
+
+    from .attention import FlashDisentangledSelfAttention
+
+    class Cfg:
+        hidden_size = H * 64
+        num_attention_heads = H
+        attention_probs_dropout_prob = 0.0
+        hidden_dropout_prob = 0.0
+        pos_att_type = ["c2p", "p2c"]
+        relative_attention = True
+        position_buckets = 256
+        max_relative_positions = 512
+        max_position_embeddings = 512
+        share_att_key = True
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    eager = DisentangledSelfAttention(Cfg()).eval().to(dev)
+    flash = FlashDisentangledSelfAttention(Cfg()).eval().to(dev)
+    flash.load_state_dict(eager.state_dict())
+    flash = flash.to(torch.bfloat16)
+    x = torch.randn(B, L, H * 64, device=dev)
+    rel = torch.randn(512, H * 64, device=dev) * 0.02
+    mask2 = torch.ones(B, L, device=dev)
+    mask4 = mask2[:, None, None, :] * mask2[:, None, :, None]
+    res = {"op": "eager_gpu", "batch": B, "seq": L, "heads": H}
+    f = attn_flops([L] * B, H)
+    with torch.no_grad():
+        for name, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+            m = eager.to(dt)
+            xx, rr, mm = x.to(dt), rel.to(dt), mask4.to(dt)
+            med, _ = _time(lambda i: m(xx, mm, rel_embeddings=rr), iters, warmup)
+            res[f"eager_{name}_ms"] = med
+            res[f"eager_{name}_attn_tflops"] = f / med / 1e9
+        xb, rb = x.bfloat16(), rel.bfloat16()
+        med, _ = _time(lambda i: flash(xb, mask2, rel_embeddings=rb), iters, warmup)
+        res["fused_module_bf16_ms"] = med
+        res["fused_module_attn_tflops"] = f / med / 1e9
+    ops.check_status()
+    res["note"] = "whole attention module incl. q/k/v and position projections; TFLOP/s divides the attention FLOPs only"
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=8)
@@ -94,10 +225,18 @@ def main():
     ap.add_argument("--valid", type=int, default=0, help="valid length of every sequence (default: all)")
     ap.add_argument("--add-layernorm", action="store_true", help="time fdb_add_layernorm instead of the attention")
     ap.add_argument("--linear-gelu", action="store_true", help="time fdb_linear_gelu (rows x hidden -> out-features)")
+    ap.add_argument("--eager-gpu", action="store_true",
+                    help="time transformers' eager attention module on the GPU (fp32, bf16) beside this package's module")
+    ap.add_argument("--reference-triton", action="store_true",
+                    help="time the reference's bias GEMMs + Triton kernel beside the fused call on the same inputs")
     ap.add_argument("--out-features", type=int, default=3072)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--hidden", type=int, default=768)
     args = ap.parse_args()
+    if args.eager_gpu:
+        return bench_eager_gpu(args.batch, args.seq, args.heads, args.iters, args.warmup)
+    if args.reference_triton:
+        return bench_reference_triton(args.batch, args.seq, args.heads, args.iters, args.warmup, args.sets)
     if args.linear_gelu:
         return bench_linear_gelu(args.rows, args.hidden, args.out_features, args.iters, args.warmup, args.sets)
     if args.add_layernorm:

@@ -158,9 +158,9 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         if self.training or torch.is_grad_enabled() or not self.relative_attention:
             return super().get_rel_embedding()
         w = self.rel_embeddings.weight
-        key = [w.data_ptr(), w._version, w.dtype, w.device]
+        key = [ops.tensor_stamp(w, held=True), w.dtype, w.device]
         if "layer_norm" in self.norm_rel_ebd:
-            key += [self.LayerNorm.weight._version, self.LayerNorm.bias._version, self.LayerNorm.weight.data_ptr()]
+            key += [ops.tensor_stamp(self.LayerNorm.weight, held=True), ops.tensor_stamp(self.LayerNorm.bias, held=True)]
         if self._rel_cache is None or self._rel_cache[0] != key:
             self._rel_cache = (key, super().get_rel_embedding())
         return self._rel_cache[1]
@@ -173,32 +173,38 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
                                    query_states, relative_pos, return_dict)
         # What the mask says (lengths, padding or not, the packing indices) is worked out once per mask tensor: the same
         # tensor, unmodified, coming back (a serving loop with a resident mask) costs no kernels and no host read.
-        key = (attention_mask.data_ptr(), attention_mask._version, tuple(attention_mask.shape), attention_mask.dtype)
+        stamp = ops.tensor_stamp(attention_mask)  # None for a mask without a version counter: analysed on every call
+        key = (stamp, tuple(attention_mask.shape), attention_mask.dtype)
         cached = self._mask_cache
         if host_mask is not None:
             dev = hidden_states.device if torch.is_tensor(hidden_states) else attention_mask.device
             input_mask = attention_mask if attention_mask.dim() <= 2 else attention_mask.sum(-2) > 0
-            seq_lens = lengths_from_mask(host_mask).to(dev, non_blocking=True)
             packed_all, looked = None, False
             if getattr(self.config_pack, "pack_sequences", True) and self.conv is None and input_mask.dim() == 2:
                 host2d = host_mask if host_mask.dim() <= 2 else host_mask.sum(-2) > 0
                 packed_all, looked = PackedSequences.from_mask(host2d, device=dev), True
-        elif cached is not None and cached[0] == key and cached[1] is attention_mask:
+            # a batch that stays padded is addressed by lengths alone: its mask must be right-padded (checked here)
+            seq_lens = lengths_from_mask(host_mask, check=packed_all is None).to(dev, non_blocking=True)
+        elif stamp is not None and cached is not None and cached[0] == key and cached[1] is attention_mask:
             input_mask, seq_lens, packed_all, looked = cached[2]
         else:
             if attention_mask.dim() <= 2:
                 input_mask = attention_mask
             else:
                 input_mask = attention_mask.sum(-2) > 0
-            seq_lens = lengths_from_mask(attention_mask)  # (B,) int32; the only form of the mask the layers see
             # Ragged batch: run the whole stack on packed tokens.  (The convolution of the v2-xlarge models needs the
             # padded layout.)
             packed_all, looked = None, False
             if getattr(self.config_pack, "pack_sequences", True) and self.conv is None and input_mask.dim() == 2:
                 packed_all, looked = PackedSequences.from_mask(input_mask), True
+            # (B,) int32; the only form of the mask the layers see.  A batch that stays padded is addressed by lengths
+            # alone: its mask must be right-padded (checked here; the packed path takes any layout)
+            seq_lens = lengths_from_mask(attention_mask, check=packed_all is None)
             self._mask_cache = (key, attention_mask, (input_mask, seq_lens, packed_all, looked))
         # query_states / a list of hidden states are only used by z_steps: those stay padded
         packed = packed_all if (query_states is None and torch.is_tensor(hidden_states)) else None
+        if packed is None and packed_all is not None:
+            seq_lens = lengths_from_mask(attention_mask)  # stays padded after all: the mask must be right-padded
         if looked and packed_all is None:
             seq_lens = None  # no padding anywhere (from_mask has looked): the layers' tile order can be kept
         if packed is not None:
@@ -226,15 +232,19 @@ class FlashDebertaV2Encoder(DebertaV2Encoder):
         return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden_states, attentions=None)
 
     def _forward_packed(self, hidden_states, packed: PackedSequences, output_hidden_states, return_dict):
+        """Every layer on the (1, T, hidden) row of valid tokens.  ``packed.indices`` None: the input already is that row
+        (the caller handed the model packed ids and cu_seqlens) and so is the output."""
+        already = packed.indices is None
+        unpack = (lambda t: t) if already else packed.unpack
         all_hidden_states = (hidden_states,) if output_hidden_states else None
-        x = packed.pack(hidden_states)  # (1, T, hidden)
+        x = hidden_states if already else packed.pack(hidden_states)  # (1, T, hidden)
         rel_embeddings = self.get_rel_embedding()
         for layer_module in self.layer:
             x, _ = layer_module(x, packed, query_states=None, relative_pos=None, rel_embeddings=rel_embeddings,
                                 output_attentions=False)
             if output_hidden_states:
-                all_hidden_states = all_hidden_states + (packed.unpack(x),)
-        output_states = all_hidden_states[-1] if output_hidden_states else packed.unpack(x)
+                all_hidden_states = all_hidden_states + (unpack(x),)
+        output_states = all_hidden_states[-1] if output_hidden_states else unpack(x)
         if not return_dict:
             return tuple(v for v in [output_states, all_hidden_states, None] if v is not None)
         return BaseModelOutput(last_hidden_state=output_states, hidden_states=all_hidden_states, attentions=None)
@@ -258,16 +268,24 @@ class FlashDebertaV2Model(DebertaV2Model):
     def forward(self, input_ids: Optional[torch.Tensor] = None, attention_mask: Optional[torch.Tensor] = None,
                 token_type_ids: Optional[torch.Tensor] = None, position_ids: Optional[torch.Tensor] = None,
                 inputs_embeds: Optional[torch.Tensor] = None, output_attentions: Optional[bool] = None,
-                output_hidden_states: Optional[bool] = None, return_dict: Optional[bool] = None, **kwargs):
+                output_hidden_states: Optional[bool] = None, return_dict: Optional[bool] = None,
+                cu_seqlens: Optional[torch.Tensor] = None, max_seqlen: Optional[int] = None, **kwargs):
         """Same arguments and outputs as src/flashdeberta/model.py:418-496; the encoder is only asked for every layer's
-        hidden states when the caller wants them (the reference always collects them, model.py:463-467)."""
+        hidden states when the caller wants them (the reference always collects them, model.py:463-467).
+
+        Packed input (no counterpart in the reference's model, whose varlen path starts from a padded batch in every
+        layer, model.py:206-249): ``input_ids`` (1, T) or (T,) holding the tokens of all sequences back to back,
+        ``cu_seqlens`` (B+1,) int32 with sequence b at [cu_seqlens[b], cu_seqlens[b+1]) and ``max_seqlen`` >= every length.
+        Nothing of size (B, L_max) is ever built; ``last_hidden_state`` comes back as (1, T, hidden).
+
+        ``z_steps`` > 1 (set on the instance; transformers' constructor leaves it 0, src/flashdeberta/model.py:404) runs
+        the last layer again z_steps - 1 times with the previous output as the queries over the keys and values of the
+        layer before, which is what model.py:469-485 means to do (as written it appends to a tuple and raises)."""
         if not self.encoder._fused:
             return super().forward(input_ids=input_ids, attention_mask=attention_mask, token_type_ids=token_type_ids,
                                    position_ids=position_ids, inputs_embeds=inputs_embeds,
                                    output_attentions=output_attentions, output_hidden_states=output_hidden_states,
                                    return_dict=return_dict, **kwargs)
-        if self.z_steps > 1:
-            raise NotImplementedError("z_steps > 1 is not supported with the fused attention backend")
         if output_attentions if output_attentions is not None else self.config.output_attentions:
             raise ValueError("the fused attention never materialises attention probabilities")
         output_hidden_states = (output_hidden_states if output_hidden_states is not None
@@ -281,6 +299,9 @@ class FlashDebertaV2Model(DebertaV2Model):
             input_shape, device = inputs_embeds.size()[:-1], inputs_embeds.device
         else:
             raise ValueError("You have to specify either input_ids or inputs_embeds")
+        if cu_seqlens is not None:
+            return self._forward_packed_ids(input_ids, inputs_embeds, cu_seqlens, max_seqlen, output_hidden_states,
+                                            return_dict)
         host_mask = None
         if attention_mask is None:
             attention_mask = torch.ones(input_shape, device=device)
@@ -293,12 +314,47 @@ class FlashDebertaV2Model(DebertaV2Model):
             token_type_ids = torch.zeros(input_shape, dtype=torch.long, device=device)
         embedding_output = self.embeddings(input_ids=input_ids, token_type_ids=token_type_ids,
                                            position_ids=position_ids, mask=attention_mask, inputs_embeds=inputs_embeds)
-        enc = self.encoder(embedding_output, attention_mask, output_hidden_states=bool(output_hidden_states),
+        z_extra = self.z_steps > 1
+        enc = self.encoder(embedding_output, attention_mask, output_hidden_states=bool(output_hidden_states) or z_extra,
                            output_attentions=False, return_dict=True, host_mask=host_mask)
+        last, hidden = enc.last_hidden_state, enc.hidden_states
+        if z_extra:
+            kv, query = hidden[-2], hidden[-1]
+            rel_embeddings = self.encoder.get_rel_embedding()
+            seq_lens = lengths_from_mask(host_mask if host_mask is not None else attention_mask)
+            if seq_lens is not None:
+                seq_lens = seq_lens.to(device, non_blocking=True)
+            for _ in range(self.z_steps - 1):
+                query, _ = self.encoder.layer[-1](kv, seq_lens, query_states=query, relative_pos=None,
+                                                  rel_embeddings=rel_embeddings, output_attentions=False)
+                hidden = hidden + (query,)
+            last = query
         if not return_dict:
-            return (enc.last_hidden_state,) + ((enc.hidden_states,) if output_hidden_states else ())
-        return BaseModelOutput(last_hidden_state=enc.last_hidden_state,
-                               hidden_states=enc.hidden_states if output_hidden_states else None, attentions=None)
+            return (last,) + ((hidden,) if output_hidden_states else ())
+        return BaseModelOutput(last_hidden_state=last, hidden_states=hidden if output_hidden_states else None,
+                               attentions=None)
+
+    def _forward_packed_ids(self, input_ids, inputs_embeds, cu_seqlens, max_seqlen, output_hidden_states, return_dict):
+        if self.z_steps > 1:
+            raise ValueError("z_steps > 1 needs the padded form of the batch")
+        if self.encoder.conv is not None:
+            raise ValueError("the convolution layer of this configuration needs the padded form of the batch")
+        if max_seqlen is None:
+            raise ValueError("packed input needs max_seqlen (an upper bound on every sequence length) beside cu_seqlens")
+        x = input_ids if input_ids is not None else inputs_embeds
+        if input_ids is not None and input_ids.dim() == 1:
+            input_ids = input_ids.unsqueeze(0)
+        if inputs_embeds is not None and inputs_embeds.dim() == 2:
+            inputs_embeds = inputs_embeds.unsqueeze(0)
+        rows = (input_ids if input_ids is not None else inputs_embeds).shape[:2]
+        if rows[0] != 1:
+            raise ValueError("packed input is one row of tokens: input_ids (1, T) or (T,)")
+        device = x.device
+        cu = cu_seqlens.to(device=device, dtype=torch.int32)
+        embedding_output = self.embeddings(input_ids=input_ids, token_type_ids=None, position_ids=None, mask=None,
+                                           inputs_embeds=inputs_embeds)
+        packed = PackedSequences(cu, int(max_seqlen), None, cu.numel() - 1, rows[1])
+        return self.encoder._forward_packed(embedding_output, packed, bool(output_hidden_states), return_dict)
 
 
 def _with_flash_backbone(hf_cls, doc):

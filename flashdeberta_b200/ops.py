@@ -53,7 +53,28 @@ def check_status(device=None) -> None:
                 what.append("cu_seqlens/seq_lens hold a length below zero or above max_seqlen")
             if v & _lib.FDB_DEV_BAD_INDEX:
                 what.append("an input id lies outside the embedding table")
+            if v & _lib.FDB_DEV_BAD_MASK:
+                what.append("a dense attention mask was not right-padded (valid tokens must be a prefix of each row; "
+                            "pack the batch to use other layouts)")
             raise RuntimeError("flashdeberta_b200 device status %d: %s" % (v, "; ".join(what)))
+
+
+def tensor_stamp(t: Optional[torch.Tensor], held: bool = False):
+    """(address, version counter) of a tensor: equal stamps of the same live tensor mean "not modified in place since".
+    Tensors made under ``torch.inference_mode()`` keep no version counter (reading it raises).  For those the stamp is the
+    object's identity when the caller keeps a reference to the tensor (``held``: the address cannot be reused, and such
+    tensors cannot be written outside inference mode), else None, which callers treat as "changed"."""
+    if t is None:
+        return None
+    if t.is_inference():
+        return ("inference", id(t), t.data_ptr()) if held else None
+    return (t.data_ptr(), t._version)
+
+
+def flag_status(device: torch.device, condition: torch.Tensor, bit: int) -> None:
+    """OR ``bit`` into the device status word where the 0-d boolean ``condition`` (on that device) is true.  No host
+    synchronisation: the word is read by ``check_status``."""
+    _status_word(device).bitwise_or_(condition.to(torch.int32) * bit)
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -175,12 +196,15 @@ def disentangled_attention(
     *, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None,
     max_seqlen: int, sm_scale: Optional[float] = None, position_buckets: int = -1, max_relative_positions: int = -1,
     return_lse: bool = False, scales: Optional[dict] = None, prepared: Optional[PreparedWorkspace] = None,
+    tune: int = 0,
 ):
     """softmax((Q K^T + c2p + p2c) * sm_scale) V on the fused sm_100a kernel.
 
     q, k, v: (B, L, H, 64) [dense, right-padded, lengths in ``seq_lens`` or all L] or (T, H, 64) [packed, with
     ``cu_seqlens``]; bf16 (or float8_e4m3fn with ``scales``).  pos_key / pos_query: (H, 2*att_span, 64) projected
     relative-position tables or None.  Returns bf16 of q's shape (and the natural-log LSE (rows, H) when asked).
+    ``tune``: ``_lib.TUNE_*`` bits that force which kernels the call is split into (tests and tuning runs; 0 = the
+    library chooses).
     """
     global _launches
     if not q.is_cuda:
@@ -195,6 +219,7 @@ def disentangled_attention(
     with torch.cuda.device(q.device):
         p, keep = _fill_params(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale,
                                position_buckets, max_relative_positions, out, lse, scales)
+        p.tune = int(tune)
         need = lib.fdb_attn_workspace_bytes(C.byref(p))
         if need == 0:  # invalid parameters (raises with the library's message) or an empty batch
             _lib.check(lib.fdb_attn_fwd(C.byref(p), None))
@@ -205,16 +230,18 @@ def disentangled_attention(
             prepared.stream = stream  # the buffer stays with the first stream that used it; other streams take scratch
             layout = (q.device, stream, need, p.dtype, p.batch, p.max_seqlen, p.total_rows, p.heads, int(position_buckets),
                       int(max_relative_positions), cu_seqlens is not None)
-            tables = tuple((t.data_ptr(), t._version) if t is not None else None for t in (pos_key, pos_query))
+            tables = tuple(tensor_stamp(t, held=True) for t in (pos_key, pos_query))  # kept alive in `prepared.keep`
+            if any(s is None and t is not None for s, t in zip(tables, (pos_key, pos_query))):
+                tables = None  # a table without a version counter: gathered again on every call
             lens_t = cu_seqlens if cu_seqlens is not None else seq_lens
             # the lengths behind the tile order: none (an unpadded batch), or this very tensor, unmodified
-            full = ("full",) if lens_t is None else (lens_t.data_ptr(), lens_t._version)
+            full = ("full",) if lens_t is None else tensor_stamp(lens_t)
             if prepared.buf is None or prepared.layout != layout:
                 prepared.buf = torch.empty(need + 256, dtype=torch.uint8, device=q.device)
             else:
-                if prepared.schedule == full:
+                if full is not None and prepared.schedule == full:
                     flags |= _lib.PREPARED_SCHEDULE
-                if prepared.tables == tables and tables != (None, None):
+                if tables is not None and prepared.tables == tables and tables != (None, None):
                     flags |= _lib.PREPARED_TABLES
             prepared.layout, prepared.schedule, prepared.tables, prepared.keep = None, None, None, None
             ws = prepared.buf
@@ -361,7 +388,7 @@ def quantize_e4m3(x: torch.Tensor, slab_start: torch.Tensor) -> Tuple[torch.Tens
     scale = torch.empty(n, H, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         stream = torch.cuda.current_stream(x.device).cuda_stream
-        _lib.check(lib.fdb_quantize_e4m3(x3.data_ptr(), rs, hs, slab_start.data_ptr(), n, H, D, y.data_ptr(),
+        _lib.check(lib.fdb_quantize_e4m3(x3.data_ptr(), rows, rs, hs, slab_start.data_ptr(), n, H, D, y.data_ptr(),
                                          scale.data_ptr(), C.c_void_p(stream)))
         _launches += 1
     return y.view(x.shape), scale

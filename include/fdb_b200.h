@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define FDB_ABI_VERSION 2
+#define FDB_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define FDB_API __attribute__((visibility("default")))
@@ -49,6 +49,8 @@ typedef enum fdb_dtype {
 #define FDB_DEV_TIMEOUT 1u      /* a bounded wait inside a kernel ran out; the output is invalid */
 #define FDB_DEV_BAD_SEQLEN 2u   /* cu_seqlens not monotone / a length below zero or above max_seqlen */
 #define FDB_DEV_BAD_INDEX 4u    /* fdb_embed_layernorm met an id outside the table (the row was taken from its edge) */
+#define FDB_DEV_BAD_MASK 8u     /* reserved for callers: the Python layer sets it when a dense attention mask on the device is
+                                   not a right-padded prefix (dense rows are addressed by length alone) */
 
 /*
  * One attention call.  Replaces, in one launch sequence, what the reference does in
@@ -130,10 +132,20 @@ typedef struct fdb_attn_params {
    * flash_attention_varlen.py:71-83; the index arithmetic per score element, flash_attention.py:236-254).  0: nothing
    * is assumed. */
   uint32_t prepared;
+
+  /* FDB_TUNE_* bits: overrides of choices the library otherwise makes from the shapes (which kernels a call is split
+   * into).  The result is the same either way; they exist so that a test or a tuning run can reach every kernel at any
+   * size.  0: the library chooses. */
+  uint32_t tune;
 } fdb_attn_params;
 
 #define FDB_PREPARED_SCHEDULE 1u
 #define FDB_PREPARED_TABLES 2u
+
+#define FDB_TUNE_ONE_LAUNCH 1u     /* every key tile in the fused kernel, whatever the length */
+#define FDB_TUNE_TWO_LAUNCHES 2u   /* far key tiles in the far kernel first, band tiles after (bf16 with position terms) */
+#define FDB_TUNE_FAR_ONE_TEAM 4u   /* far kernel: one softmax team per CTA, two CTAs per SM */
+#define FDB_TUNE_FAR_TWO_TEAMS 8u  /* far kernel: two softmax teams in one CTA */
 
 /* Library / ABI version (FDB_ABI_VERSION the library was built with). */
 FDB_API int fdb_abi_version(void);
@@ -182,13 +194,18 @@ FDB_API int fdb_attn_fwd(const fdb_attn_params* p, void* stream);
  * caller's.  It calls no cudaMalloc, cudaFree or any other allocating routine.
  *
  * Limits and rules:
- *  - parameters whose scratch need (fdb_attn_workspace_bytes) exceeds FDB_STATIC_SCRATCH_BYTES are refused with
- *    FDB_ERR_LIMIT and nothing is launched (DeBERTa-v3 geometry: up to 16 heads and tens of thousands of sequences fit);
+ *  - this entry point always runs the call as one launch of the fused kernel, so its scratch need is the sequence table,
+ *    the tile order and the two gathered tables only: what fdb_attn_workspace_bytes reports with FDB_TUNE_ONE_LAUNCH set
+ *    in p->tune (without that bit the query adds, from 3584 keys, the partial-result buffers of the two-launch form, which
+ *    are not used here).  Parameters that need more than FDB_STATIC_SCRATCH_BYTES are refused with FDB_ERR_LIMIT and
+ *    nothing is launched (DeBERTa-v3 geometry: up to 16 heads and tens of thousands of sequences fit);
  *  - the first call on each device looks the array's device address up once (with that device current); make that
  *    first call outside any stream capture;
  *  - every call on a device uses the same array and leaves its contents behind.  The kernels rewrite every byte
  *    they later read, so nothing has to be cleared between calls, but two calls that overlap on the GPU (different
- *    streams, or different host threads without ordering) race on it: keep calls on one device ordered.
+ *    streams, or different host threads without ordering) race on it: keep calls on one device ordered;
+ *  - the looked-up address is kept for the life of the process.  cudaDeviceReset() on a device that has already made a
+ *    call leaves that address dangling: do not reset a device between calls to this entry point.
  */
 #define FDB_STATIC_SCRATCH_BYTES (8u << 20)
 FDB_API int fdb_attn_fwd_static(const fdb_attn_params* p, void* stream);
@@ -211,11 +228,13 @@ FDB_API int fdb_relative_index_matrix(const int16_t* bucket_lut, int32_t lut_d_m
 /*
  * Per-slab amax scaling to e4m3 (no counterpart in the reference; the FP8 option of this library).
  * x is (rows, heads, head_dim) strided like q; slab s covers rows [slab_start[s], slab_start[s+1]) of one head
- * (slab_start device int32, n_slabs+1 entries; pass the cu_seqlens array).  Writes y (e4m3, contiguous
- * (rows, heads, head_dim)) and scale[s*heads + h] = amax/448.
+ * (slab_start device int32, n_slabs+1 entries; pass the cu_seqlens array); slab bounds are clamped to [0, rows).
+ * Writes y (e4m3, contiguous (rows, heads, head_dim)) and scale[s*heads + h] = amax/448.
+ * x must be 16-byte aligned, y 8-byte aligned, the strides positive multiples of 8 elements (FDB_ERR_ALIGNMENT).
  */
-FDB_API int fdb_quantize_e4m3(const void* x_bf16, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,
-                      int32_t n_slabs, int32_t heads, int32_t head_dim, void* y_e4m3, float* scale, void* stream);
+FDB_API int fdb_quantize_e4m3(const void* x_bf16, int64_t rows, int64_t row_stride, int64_t head_stride,
+                      const int32_t* slab_start, int32_t n_slabs, int32_t heads, int32_t head_dim, void* y_e4m3,
+                      float* scale, void* stream);
 
 /*
  * out = LayerNorm(x + residual) over the last dimension (eps inside the square root), bf16 in and out, fp32 statistics; the

@@ -263,12 +263,12 @@ def test_fused_position_variants(c2p, p2c, buckets, max_rel):
 
 @pytest.mark.parametrize("c2p,p2c", [(True, True), (True, False), (False, True)])
 @pytest.mark.parametrize("packed", [False, True])
-@pytest.mark.parametrize("far", ["1", "2"])
+@pytest.mark.parametrize("far", [1, 2])
 @pytest.mark.parametrize("buckets,max_rel", [(256, 512), (32, 64), (-1, 96)])
-def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c, packed, far, buckets, max_rel):
-    """Sequences long enough to have saturated key tiles on both sides of the band, run with the far key tiles in the
-    two-team kernel and the band tiles in a second launch (forced through FDB_ATTN_SPLIT, which the library reads on
-    every call; long calls take this path by themselves), against the single launch and the CPU oracle."""
+def test_two_launch_path_matches_single_launch_and_oracle(c2p, p2c, packed, far, buckets, max_rel):
+    """Sequences long enough to have saturated key tiles on both sides of the band, run with the far key tiles in a far
+    kernel and the band tiles in a second launch (forced through fdb_attn_params.tune; long calls take this path by
+    themselves), against the single launch and the CPU oracle."""
     ops = _ops()
     H, D = 2, 64
     span = buckets if buckets > 0 else max_rel
@@ -289,11 +289,10 @@ def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c,
     to = lambda t: None if t is None else t.to(DEV)
     args = (to(q), to(k), to(v), to(pk), to(pq))
     kw.update(sm_scale=sm, position_buckets=buckets, max_relative_positions=max_rel, return_lse=True)
-    monkeypatch.setenv("FDB_ATTN_FAR", far)  # the far key tiles by the one-team or the two-team kernel
-    monkeypatch.setenv("FDB_ATTN_SPLIT", "1")
-    out2, lse2 = ops.disentangled_attention(*args, **kw)
-    monkeypatch.setenv("FDB_ATTN_SPLIT", "0")
-    out1, lse1 = ops.disentangled_attention(*args, **kw)
+    from flashdeberta_b200 import _lib
+    far_bit = _lib.TUNE_FAR_ONE_TEAM if far == 1 else _lib.TUNE_FAR_TWO_TEAMS  # which far kernel takes the far key tiles
+    out2, lse2 = ops.disentangled_attention(*args, tune=_lib.TUNE_TWO_LAUNCHES | far_bit, **kw)
+    out1, lse1 = ops.disentangled_attention(*args, tune=_lib.TUNE_ONE_LAUNCH, **kw)
     torch.cuda.synchronize()
     ops.check_status()
     want, want_lse = _oracle(q, k, v, pk, pq, starts, lens, sm, buckets, max_rel)
@@ -307,10 +306,10 @@ def test_two_launch_path_matches_single_launch_and_oracle(monkeypatch, c2p, p2c,
 
 
 @pytest.mark.parametrize("lens", [[1], [128], [129], [300, 129, 7], [1000, 1000], [2050, 1, 1279]])
-@pytest.mark.parametrize("far", ["1", "2"])
-def test_position_free_ragged_lengths(monkeypatch, lens, far):
+@pytest.mark.parametrize("far", [1, 2])
+def test_position_free_ragged_lengths(lens, far):
     """No position terms at all (plain softmax attention): every key tile goes through one of the two far kernels."""
-    monkeypatch.setenv("FDB_ATTN_FAR", far)
+    from flashdeberta_b200 import _lib
     ops = _ops()
     H, D = 2, 64
     q, k, v, _, _ = _random(21 + len(lens), (sum(lens),), H, 1, False, False)
@@ -321,7 +320,8 @@ def test_position_free_ragged_lengths(monkeypatch, lens, far):
     to = lambda t: t.to(DEV)
     out, lse = ops.disentangled_attention(to(q), to(k), to(v), None, None, sm_scale=sm, position_buckets=-1,
                                           max_relative_positions=-1, return_lse=True, max_seqlen=max(lens),
-                                          cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV))
+                                          cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                                          tune=_lib.TUNE_FAR_ONE_TEAM if far == 1 else _lib.TUNE_FAR_TWO_TEAMS)
     torch.cuda.synchronize()
     ops.check_status()
     want, want_lse = _oracle(q, k, v, None, None, cu[:-1], lens, sm, -1, -1)
