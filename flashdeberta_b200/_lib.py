@@ -16,7 +16,7 @@ FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN, FDB_DEV_BAD_INDEX, FDB_DEV_BAD_MASK = 1, 2,
 STATIC_SCRATCH_BYTES = 8 << 20
 ABI_VERSION = 3
 PREPARED_SCHEDULE, PREPARED_TABLES = 1, 2  # fdb_attn_params.prepared
-TUNE_ONE_LAUNCH, TUNE_TWO_LAUNCHES, TUNE_FAR_ONE_TEAM, TUNE_FAR_TWO_TEAMS = 1, 2, 4, 8  # fdb_attn_params.tune
+TUNE_ONE_LAUNCH, TUNE_TWO_LAUNCHES = 1, 2  # fdb_attn_params.tune
 
 
 class AttnParams(C.Structure):

@@ -123,7 +123,7 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         else:
             wk, wq = getattr(self, "pos_key_proj", None), getattr(self, "pos_query_proj", None)
         key = None
-        if not self.training and not torch.is_grad_enabled():
+        if not self.training and not torch.is_grad_enabled() and not torch.compiler.is_compiling():
             # the table is kept alive below, so its identity stays its own
             key = (id(rel_embeddings), ops.tensor_stamp(rel_embeddings, held=True), rel_embeddings.device, dtype,
                    tuple(ops.tensor_stamp(p, held=True) for m in (wk, wq) if m is not None for p in m.parameters()))

@@ -43,9 +43,8 @@ int validate(const fdb_attn_params* p, bool fused) {
   if (!(p->sm_scale > 0.f)) return fail(FDB_ERR_INVALID_ARGUMENT, "sm_scale must be positive");
   if ((p->prepared & ~(FDB_PREPARED_SCHEDULE | FDB_PREPARED_TABLES)) != 0)
     return fail(FDB_ERR_INVALID_ARGUMENT, "unknown bits in prepared: 0x%x", p->prepared);
-  if ((p->tune & ~(FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES | FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS)) != 0 ||
-      (p->tune & (FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES)) == (FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES) ||
-      (p->tune & (FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS)) == (FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS))
+  if ((p->tune & ~(FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES)) != 0 ||
+      (p->tune & (FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES)) == (FDB_TUNE_ONE_LAUNCH | FDB_TUNE_TWO_LAUNCHES))
     return fail(FDB_ERR_INVALID_ARGUMENT, "unknown or contradictory bits in tune: 0x%x", p->tune);
   if (p->pos_key != nullptr || p->pos_query != nullptr) {
     const int span = p->position_buckets > 0 ? p->position_buckets : p->max_relative_positions;

@@ -1,10 +1,12 @@
 // Definitions shared by the fused attention kernels (attn_fwd_sm100.cu: all tile kinds or band tiles only;
-// attn_fwd_far_sm100.cu: plain and saturated tiles, two teams in ping-pong).
+// attn_fwd_far1_sm100.cu: plain and saturated tiles, half an SM per CTA).
 #pragma once
 
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 
 #include "internal.h"
 #include "sm100_ptx.cuh"
@@ -36,6 +38,7 @@ struct alignas(64) FwdArgs {
   float* part_o;   // (rows, heads, 64)
   float* part_ml;  // (rows, heads, 2)
   int band_only;   // attn_fwd_kernel: 0 = every key tile, 1 = band tiles only (continuing from part_o / part_ml)
+  int split_len;   // two-launch calls: sequences shorter than this stay whole in attn_fwd_kernel
   int slots;       // query-tile slots of the launch (work items = slots * heads)
 #ifdef FDB_TRACE
   long long* trace;  // [role 0..3][tile 0..63][event 0..7] clock64 stamps of CTA (0, 0)
@@ -43,6 +46,12 @@ struct alignas(64) FwdArgs {
 };
 
 #ifdef FDB_TRACE
+// Development builds only (-DFDB_TRACE): clock stamps of one CTA, read back through a buffer whose address comes from the
+// environment.  Compiled out otherwise.
+inline long long* trace_buffer_from_env() {
+  const char* tp = std::getenv("FDB_TRACE_PTR");
+  return tp ? reinterpret_cast<long long*>(std::strtoull(tp, nullptr, 0)) : nullptr;
+}
 #define FDB_STAMP(role, tile, ev) \
   do { if (blockIdx.x == 0 && blockIdx.y == 0 && args.trace != nullptr && (tile) < 64) \
          args.trace[((role) * 64 + (tile)) * 8 + (ev)] = clock64(); } while (0)

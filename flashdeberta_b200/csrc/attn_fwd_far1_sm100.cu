@@ -89,7 +89,10 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_far1_kernel(const __grid
   const int num_kt = (len + kTileN - 1) / kTileN;
   // this launch's key tiles: everything outside the band run [jb, jb + nb)
   int jb = 0, nb = 0;
-  if (has_pos) band_run(m0, num_kt, args.sat_lo, args.sat_hi, jb, nb);
+  if (has_pos) {
+    if (len < args.split_len) return;  // short sequence of a two-launch call: left whole to attn_fwd_kernel
+    band_run(m0, num_kt, args.sat_lo, args.sat_hi, jb, nb);
+  }
   const int n_far = num_kt - nb;
   if (n_far <= 0) return;  // nothing but band tiles: the band kernel starts from scratch
   auto tile_of = [&](int i) -> int { return i < jb ? i : i + nb; };
@@ -251,18 +254,17 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_far1_kernel(const __grid
         }
         tmem_wait_st();
       }
-      // the team's previous P.V has finished (it was issued a whole tile of the other team ago): O_t and P_t are free
-      if (u > 0) { wait(bar(kBarO), (u - 1u) & 1u); tc_fence_after(); }
-
-      // pull the 128 scores of this row in four chunks; the maximum of the first two is taken while the rest arrive
+      // pull the 128 scores of this row in four chunks, all on their way at once
       uint32_t a0[32], a1[32], a2[32], a3[32];
       if (ok) {
         tmem_ld32(tmem_lane + kColS, a0);
         tmem_ld32(tmem_lane + kColS + 32, a1);
-        tmem_wait_ld();
         tmem_ld32(tmem_lane + kColS + 64, a2);
         tmem_ld32(tmem_lane + kColS + 96, a3);
+        tmem_wait_ld();
       }
+      tc_fence_before();
+      mbar_arrive(bar(kBarSFree));  // the scores are in registers: the next tile's may be computed
       float mx[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) mx[q] = max3(__uint_as_float(a0[q]), __uint_as_float(a0[4 + q]), __uint_as_float(a1[q]));
@@ -276,9 +278,6 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_far1_kernel(const __grid
         for (int q = 0; q < 4; ++q) mx[q] = max3(mx[q], __uint_as_float(a1[c + q]), __uint_as_float(a1[c + 4 + q]));
 #pragma unroll
       for (int q = 0; q < 4; ++q) mx[q] = fmaxf(mx[q], __uint_as_float(a1[28 + q]));
-      if (ok) tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(kBarSFree));
       if (lane == 0 && quad == 0) FDB_STAMP(0, i, 1);
 #pragma unroll
       for (int c = 0; c < 32; c += 8)
@@ -297,6 +296,8 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_far1_kernel(const __grid
       } else {
         const bool need = t_max > m_used + 8.f;
         if (__any_sync(0xffffffffu, need)) {
+          wait(bar(kBarO), (u - 1u) & 1u);  // O is only touched once the previous P.V has finished
+          tc_fence_after();
           const float m_new = fmaxf(m_used, t_max);
           const float alpha = ex2(m_used - m_new);
           l_run *= alpha;
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_far1_kernel(const __grid
       const float off = row_const * args.scale_log2 - m_used;
       const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2), off2 = pack_f32x2(off, off);
       uint64_t l2[2] = {0ull, 0ull};
-      auto half = [&](const uint32_t (&x)[32], const uint32_t (&y)[32], uint32_t col) {
+      auto half = [&](const uint32_t (&x)[32], const uint32_t (&y)[32], uint32_t col, bool first) {
         uint32_t p[32];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
@@ -333,10 +334,13 @@ __global__ void __launch_bounds__(kThreads, 2) attn_fwd_far1_kernel(const __grid
           p[c >> 1] = pack_bf16x2(e0, e1);
           p[16 + (c >> 1)] = pack_bf16x2(f0, f1);
         }
+        // P is free once the previous P.V has read it.  That P.V was issued when the previous tile's exponentials ended, so
+        // it is waited for here, behind the first 64 exponentials of this tile, and not in front of the tile
+        if (first && u > 0) { wait(bar(kBarO), (u - 1u) & 1u); tc_fence_after(); }
         if (ok) tmem_st32(tmem_lane + col, p);
       };
-      half(a0, a1, kColP);
-      half(a2, a3, kColP + 32);
+      half(a0, a1, kColP, true);
+      half(a2, a3, kColP + 32, false);
       {
         float s0, s1, s2, s3;
         unpack_f32x2(l2[0], s0, s1);

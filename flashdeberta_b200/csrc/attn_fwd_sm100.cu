@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
   const int num_kt = (len + kTileN - 1) / kTileN;
   // key tiles this launch works on: all of them, or (split launch) the contiguous run of band tiles; `jj` counts them
   int j_first = 0, n_proc = num_kt;
-  if (args.band_only) band_run(m0, num_kt, args.sat_lo, args.sat_hi, j_first, n_proc);
+  if (args.band_only && len >= args.split_len) band_run(m0, num_kt, args.sat_lo, args.sat_hi, j_first, n_proc);
   const bool resume = args.band_only && n_proc < num_kt;  // the far kernel has left a partial result for this tile
   auto tile_kind = [&](int j) -> int {
     if (!has_pos) return kPlain;
@@ -764,11 +764,9 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   a.part_o = w.split ? reinterpret_cast<float*>(ws + w.part_o) : nullptr;
   a.part_ml = w.split ? reinterpret_cast<float*>(ws + w.part_ml) : nullptr;
   a.band_only = w.split ? 1 : 0;
+  a.split_len = (p.tune & FDB_TUNE_TWO_LAUNCHES) ? 0 : kSplitSeqlen;  // forced two launches: every sequence is split
 #ifdef FDB_TRACE
-  {
-    const char* tp = std::getenv("FDB_TRACE_PTR");
-    a.trace = tp ? reinterpret_cast<long long*>(std::strtoull(tp, nullptr, 0)) : nullptr;
-  }
+  a.trace = trace_buffer_from_env();
 #endif
 
   const int64_t slots = tile_slots(p);
@@ -776,16 +774,11 @@ int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, con
   if (slots <= 0) return FDB_OK;
   if (slots > 2147483647LL || p.heads > 65535) return fail(FDB_ERR_LIMIT, "grid too large");
 
-  // bf16: key tiles with saturated (or no) position terms go to the two-team kernel; with position terms the band tiles
-  // follow in attn_fwd_kernel, which picks up the partial result on the same stream.
+  // bf16: key tiles with saturated (or no) position terms go to the far kernel (half an SM per CTA, two CTAs per SM); with
+  // position terms the band tiles follow in attn_fwd_kernel, which picks up the partial result on the same stream.
   const bool no_pos = a.xk == nullptr && a.xq == nullptr;
   if (!f8 && (w.split || (no_pos && !(p.tune & FDB_TUNE_ONE_LAUNCH)))) {
-    // Two forms of the far kernel: one team per CTA and two CTAs per SM (the start and the end of a CTA overlap the other
-    // CTA's work: better up to about 8192 keys), or two teams in one CTA with three K/V stages (better beyond).
-    // fdb_attn_params.tune can force one of them.
-    const bool one_team = (p.tune & (FDB_TUNE_FAR_ONE_TEAM | FDB_TUNE_FAR_TWO_TEAMS)) ? (p.tune & FDB_TUNE_FAR_ONE_TEAM) != 0
-                                                                                        : p.max_seqlen <= 8192;
-    rc = one_team ? launch_attn_fwd_far1(&a, slots, p.heads, stream) : launch_attn_fwd_far(&a, slots, p.heads, stream);
+    rc = launch_attn_fwd_far1(&a, slots, p.heads, stream);
     if (rc != FDB_OK) return rc;
     if (no_pos) return FDB_OK;
   }

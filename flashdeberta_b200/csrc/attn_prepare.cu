@@ -32,7 +32,7 @@ static bool want_split(const fdb_attn_params& p) {
   if (p.dtype == FDB_E4M3 || (p.pos_key == nullptr && p.pos_query == nullptr)) return false;
   if (p.tune & FDB_TUNE_ONE_LAUNCH) return false;
   if (p.tune & FDB_TUNE_TWO_LAUNCHES) return true;
-  return p.max_seqlen >= 3584;
+  return p.max_seqlen >= kSplitSeqlen;
 }
 
 int64_t tile_slots(const fdb_attn_params& p) {

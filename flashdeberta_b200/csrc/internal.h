@@ -24,6 +24,10 @@ constexpr int kTileM = 128;    // query rows per CTA tile
 constexpr int kTileN = 128;    // keys per inner step
 constexpr int kHeadDim = 64;   // the only head size the fused kernel is built for
 constexpr int kWindow = 256;   // rows of an expanded position table staged for one (query tile, key tile) pair
+// In a call that runs as two launches, only sequences of at least this many keys are split between them (shorter ones
+// have too few far key tiles to pay for it).  Deciding per sequence keeps a sequence's result independent of the batch
+// around it.
+constexpr int kSplitSeqlen = 3584;
 
 // Expanded position tables.  Row u of an expanded table holds table row idx(d) for d = d_first + u, so a tile pair
 // whose distances are [d0, d0+254] needs the contiguous rows [d0 - d_first, +255): the bucket function never runs
@@ -59,8 +63,7 @@ int64_t tile_slots(const fdb_attn_params& p);
 int launch_attn_check(const fdb_attn_params& p, void* stream);
 int launch_prepare(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
 int launch_attn_fwd_sm100(const fdb_attn_params& p, const ExpandGeometry& g, const WorkspaceLayout& w, void* stream);
-int launch_attn_fwd_far(const void* fwd_args, int64_t slots, int heads, void* stream);  // fwd_args: fwd::FwdArgs
-int launch_attn_fwd_far1(const void* fwd_args, int64_t slots, int heads, void* stream);
+int launch_attn_fwd_far1(const void* fwd_args, int64_t slots, int heads, void* stream);  // fwd_args: fwd::FwdArgs
 int launch_relative_index_matrix(const int16_t* lut, int32_t d_min, int32_t len, int32_t lq, int32_t lk, int32_t* out,
                                  void* stream);
 int launch_quantize_e4m3(const void* x, int64_t rows, int64_t row_stride, int64_t head_stride, const int32_t* slab_start,

@@ -53,6 +53,22 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parit
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_abortable_slow(bar, parity, abort_flag);
 }
+// The same for a role that is not on the critical path: it sleeps between polls, so that its polling does not take issue
+// slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_abortable_relaxed(uint32_t bar, uint32_t parity, const volatile uint32_t* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+#pragma unroll 1
+  for (uint32_t i = 0; i < (1u << 28); ++i) {
+    __nanosleep(100);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 15u) == 15u) {
+      if (*abort_flag != 0u) return false;
+      if (clock64() - t0 > 4000000000LL) break;
+    }
+  }
+  return false;
+}
 // Named barrier among `count` threads (count a multiple of 32); id 0 is __syncthreads.
 __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");

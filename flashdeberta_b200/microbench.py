@@ -221,6 +221,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated between launches")
     ap.add_argument("--no-pos", action="store_true")
+    ap.add_argument("--tune", type=int, default=0, help="fdb_attn_params.tune bits (which kernels the call is split into)")
     ap.add_argument("--fp8", action="store_true", help="e4m3 operands (quantised once, outside the timed region)")
     ap.add_argument("--valid", type=int, default=0, help="valid length of every sequence (default: all)")
     ap.add_argument("--add-layernorm", action="store_true", help="time fdb_add_layernorm instead of the attention")
@@ -252,7 +253,7 @@ def main():
     if not args.no_pos:
         pk, pq = (torch.randn(H, 512, D, generator=g).mul_(0.5).bfloat16().to(dev) for _ in range(2))
     lens = [args.valid or L] * B
-    kw = dict(max_seqlen=L, position_buckets=256, max_relative_positions=512)
+    kw = dict(max_seqlen=L, position_buckets=256, max_relative_positions=512, tune=args.tune)
     if args.valid:
         kw["seq_lens"] = torch.tensor(lens, dtype=torch.int32, device=dev)
     if args.fp8:

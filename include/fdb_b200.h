@@ -144,8 +144,6 @@ typedef struct fdb_attn_params {
 
 #define FDB_TUNE_ONE_LAUNCH 1u     /* every key tile in the fused kernel, whatever the length */
 #define FDB_TUNE_TWO_LAUNCHES 2u   /* far key tiles in the far kernel first, band tiles after (bf16 with position terms) */
-#define FDB_TUNE_FAR_ONE_TEAM 4u   /* far kernel: one softmax team per CTA, two CTAs per SM */
-#define FDB_TUNE_FAR_TWO_TEAMS 8u  /* far kernel: two softmax teams in one CTA */
 
 /* Library / ABI version (FDB_ABI_VERSION the library was built with). */
 FDB_API int fdb_abi_version(void);

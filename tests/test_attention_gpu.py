@@ -263,9 +263,8 @@ def test_fused_position_variants(c2p, p2c, buckets, max_rel):
 
 @pytest.mark.parametrize("c2p,p2c", [(True, True), (True, False), (False, True)])
 @pytest.mark.parametrize("packed", [False, True])
-@pytest.mark.parametrize("far", [1, 2])
 @pytest.mark.parametrize("buckets,max_rel", [(256, 512), (32, 64), (-1, 96)])
-def test_two_launch_path_matches_single_launch_and_oracle(c2p, p2c, packed, far, buckets, max_rel):
+def test_two_launch_path_matches_single_launch_and_oracle(c2p, p2c, packed, buckets, max_rel):
     """Sequences long enough to have saturated key tiles on both sides of the band, run with the far key tiles in a far
     kernel and the band tiles in a second launch (forced through fdb_attn_params.tune; long calls take this path by
     themselves), against the single launch and the CPU oracle."""
@@ -290,8 +289,7 @@ def test_two_launch_path_matches_single_launch_and_oracle(c2p, p2c, packed, far,
     args = (to(q), to(k), to(v), to(pk), to(pq))
     kw.update(sm_scale=sm, position_buckets=buckets, max_relative_positions=max_rel, return_lse=True)
     from flashdeberta_b200 import _lib
-    far_bit = _lib.TUNE_FAR_ONE_TEAM if far == 1 else _lib.TUNE_FAR_TWO_TEAMS  # which far kernel takes the far key tiles
-    out2, lse2 = ops.disentangled_attention(*args, tune=_lib.TUNE_TWO_LAUNCHES | far_bit, **kw)
+    out2, lse2 = ops.disentangled_attention(*args, tune=_lib.TUNE_TWO_LAUNCHES, **kw)
     out1, lse1 = ops.disentangled_attention(*args, tune=_lib.TUNE_ONE_LAUNCH, **kw)
     torch.cuda.synchronize()
     ops.check_status()
@@ -306,9 +304,10 @@ def test_two_launch_path_matches_single_launch_and_oracle(c2p, p2c, packed, far,
 
 
 @pytest.mark.parametrize("lens", [[1], [128], [129], [300, 129, 7], [1000, 1000], [2050, 1, 1279]])
-@pytest.mark.parametrize("far", [1, 2])
-def test_position_free_ragged_lengths(lens, far):
-    """No position terms at all (plain softmax attention): every key tile goes through one of the two far kernels."""
+@pytest.mark.parametrize("one_launch", [False, True])
+def test_position_free_ragged_lengths(lens, one_launch):
+    """No position terms at all (plain softmax attention): every key tile goes through the far kernel, or (forced) through
+    the fused kernel."""
     from flashdeberta_b200 import _lib
     ops = _ops()
     H, D = 2, 64
@@ -321,7 +320,7 @@ def test_position_free_ragged_lengths(lens, far):
     out, lse = ops.disentangled_attention(to(q), to(k), to(v), None, None, sm_scale=sm, position_buckets=-1,
                                           max_relative_positions=-1, return_lse=True, max_seqlen=max(lens),
                                           cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=DEV),
-                                          tune=_lib.TUNE_FAR_ONE_TEAM if far == 1 else _lib.TUNE_FAR_TWO_TEAMS)
+                                          tune=_lib.TUNE_ONE_LAUNCH if one_launch else 0)
     torch.cuda.synchronize()
     ops.check_status()
     want, want_lse = _oracle(q, k, v, None, None, cu[:-1], lens, sm, -1, -1)
