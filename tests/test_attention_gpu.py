@@ -528,7 +528,8 @@ def test_sharded_ragged_batch_matches_whole_batch():
             sid, smask, owned = shard_batch(ids, mask, rank, 3)
             assert owned == partition_by_tokens(lens, 3)[rank]
             h = model(input_ids=sid, attention_mask=smask).last_hidden_state
-            out += gather_sequences(h, owned, B, L)
+            for row, b in enumerate(owned):  # what the final exchange does, on one device
+                out[b, :lens[b]] = h[row, :lens[b]]
     d = (out.float() - whole.float()).abs()
     assert d.max().item() < 0.1 and d.mean().item() < 5e-3, (d.max().item(), d.mean().item())
 

@@ -7,7 +7,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from flashdeberta_b200.dist import gather_sequences, partition_by_tokens, shard_batch
+from flashdeberta_b200.dist import (ShardPlan, gather_packed, gather_sequences, partition_by_tokens,
+                                    quadratic_weight_from_times, shard_batch)
 
 
 def _config3_lengths():
@@ -77,8 +78,14 @@ def _worker(rank, world, port, lens, fail_rank):
         if any(s != "ok" for s in status):
             assert status[fail_rank].startswith("error")
             return
-        out = gather_sequences(local, owned, B, L)
+        out = gather_sequences(local, lens, L, rank, world)
         assert torch.equal(out, full)
+        # the packed form of the same exchange: only valid rows travel, padded to the largest shard
+        plan = ShardPlan(lens, world)
+        packed_full = torch.cat([full[b, :n] for b, n in enumerate(lens)])
+        mine = packed_full[plan.local_rows(rank)]
+        assert mine.shape[0] == plan.tokens[rank] == sum(lens[i] for i in owned)
+        assert torch.equal(gather_packed(mine, plan), packed_full)
     finally:
         dist.destroy_process_group()
 
@@ -86,3 +93,26 @@ def _worker(rank, world, port, lens, fail_rank):
 @pytest.mark.parametrize("lens,fail_rank", [([9, 3, 5, 1, 7], -1), ([4], -1), ([6, 6, 2], 1)])
 def test_two_rank_gather_on_gloo(lens, fail_rank):
     mp.spawn(_worker, args=(2, _free_port(), lens, fail_rank), nprocs=2, join=True)
+
+
+def test_shard_plan_and_cost_weight():
+    lens = _config3_lengths()
+    plan = ShardPlan(lens, 8)
+    assert sum(plan.tokens) == plan.total == 350907 and plan.max_tokens / (plan.total / 8) < 1.001
+    rows = torch.cat([plan.local_rows(r) for r in range(8)])
+    assert torch.equal(torch.sort(rows).values, torch.arange(plan.total))  # every row owned exactly once
+    perm = plan.gather_permutation("cpu")
+    assert perm.numel() == plan.total and len(set(perm.tolist())) == plan.total
+    for r in range(8):
+        cu = plan.cu_seqlens(r)
+        assert cu[-1] == plan.tokens[r] and len(cu) == len(plan.bins[r]) + 1
+        assert plan.max_seqlen(r) == max(lens[i] for i in plan.bins[r])
+    # a step whose attention (all of it quadratic here: no position terms counted) takes half of the time
+    w = quadratic_weight_from_times(10.0, 5.0, [1000] * 4, att_span=0)
+    assert abs(w - 1 / 1000) < 1e-9
+    # with that weight the quadratic part of the cost is balanced too
+    w = quadratic_weight_from_times(100.0, 60.0, lens)
+    bins = partition_by_tokens(lens, 8, quadratic_weight=w)
+    quad = [sum(lens[i] ** 2 for i in b) for b in bins]
+    cost = [sum(lens[i] + w * lens[i] ** 2 for i in b) for b in bins]
+    assert max(cost) / (sum(cost) / 8) < 1.01 and max(quad) / (sum(quad) / 8) < 1.06
