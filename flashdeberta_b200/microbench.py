@@ -212,6 +212,27 @@ def bench_eager_gpu(B: int, L: int, H: int, iters: int, warmup: int):
     print(json.dumps(res))
 
 
+def bench_packed256(H: int, iters: int, warmup: int, tune: int):
+    """The fused attention on the packed benchmark batch: 256 sequences with lengths log-uniform in [64, 8192] (seed 2,
+    350907 tokens) behind one cu_seqlens, c2p + p2c, bf16."""
+    import math
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(2)
+    u = torch.rand(256, dtype=torch.float64, generator=g)
+    lens = torch.floor(torch.exp(math.log(64) + u * (math.log(8192) - math.log(64)))).long().tolist()
+    T, D = sum(lens), 64
+    gd = torch.Generator(device=dev).manual_seed(2)
+    sets = [tuple(torch.randn(T, H, D, generator=gd, device=dev).bfloat16() for _ in range(3)) for _ in range(2)]
+    pk, pq = (torch.randn(H, 512, D, generator=gd, device=dev).mul_(0.5).bfloat16() for _ in range(2))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    kw = dict(cu_seqlens=cu, max_seqlen=max(lens), position_buckets=256, max_relative_positions=512, tune=tune)
+    med, mn = _time(lambda i: ops.disentangled_attention(*sets[i % 2], pk, pq, **kw), iters, warmup)
+    ops.check_status()
+    f = attn_flops(lens, H)
+    print(json.dumps({"workload": "packed 256 sequences, 350907 tokens", "heads": H, "ms_median": med, "ms_min": mn,
+                      "tflops_median": f / med / 1e9, "flops": f}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=8)
@@ -221,6 +242,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--sets", type=int, default=4, help="independent input sets rotated between launches")
     ap.add_argument("--no-pos", action="store_true")
+    ap.add_argument("--packed256", action="store_true", help="the packed 256-sequence benchmark batch (use --heads 16)")
     ap.add_argument("--tune", type=int, default=0, help="fdb_attn_params.tune bits (which kernels the call is split into)")
     ap.add_argument("--fp8", action="store_true", help="e4m3 operands (quantised once, outside the timed region)")
     ap.add_argument("--valid", type=int, default=0, help="valid length of every sequence (default: all)")
@@ -243,6 +265,8 @@ def main():
     if args.add_layernorm:
         return bench_add_layernorm(args.rows, args.hidden, args.iters, args.warmup, max(args.sets, 8))
     dev = torch.device("cuda")
+    if args.packed256:
+        return bench_packed256(args.heads, args.iters, args.warmup, args.tune)
     B, L, H, D = args.batch, args.seq, args.heads, 64
     g = torch.Generator(device="cpu").manual_seed(0)
     sets = []
