@@ -179,6 +179,27 @@ def test_layer_output_blocks_keep_transformers_parameter_names():
         assert torch.equal(ours.intermediate(x), theirs.intermediate(x))
 
 
+@pytest.mark.parametrize("x,rows,row_stride,head_stride,y,head_dim,code", [
+    (0, 4, 768, 64, 0x2000, 64, -1),         # x NULL
+    (0x1000, -1, 768, 64, 0x2000, 64, -1),   # negative row count
+    (0x1000, 4, 768, 64, 0x2000, 60, -1),    # head_dim not a multiple of 8
+    (0x1008, 4, 768, 64, 0x2000, 64, -3),    # x not 16-byte aligned
+    (0x1000, 4, 768, 64, 0x2004, 64, -3),    # y not 8-byte aligned
+    (0x1000, 4, 772, 64, 0x2000, 64, -3),    # row stride not a multiple of 8 elements
+    (0x1000, 4, 768, 0, 0x2000, 64, -3),     # head stride not positive
+])
+def test_quantize_argument_errors(x, rows, row_stride, head_stride, y, head_dim, code):
+    lib = _lib.load()
+    rc = lib.fdb_quantize_e4m3(x or None, rows, row_stride, head_stride, 0x3000, 1, 12, head_dim, y, 0x4000, None)
+    assert rc == code
+    assert lib.fdb_last_error().decode() != ""
+
+
+def test_quantize_zero_rows_is_a_no_op():
+    lib = _lib.load()
+    assert lib.fdb_quantize_e4m3(0x1000, 0, 768, 64, 0x3000, 1, 12, 64, 0x2000, 0x4000, None) == 0
+
+
 @pytest.mark.parametrize("x,weight,k,n,code", [
     (0, 0x1000, 768, 3072, -1),        # x NULL
     (0x1000, 0, 768, 3072, -1),        # weight NULL
