@@ -14,7 +14,7 @@ FDB_OK = 0
 FDB_BF16, FDB_FP32, FDB_E4M3 = 0, 1, 2
 FDB_DEV_TIMEOUT, FDB_DEV_BAD_SEQLEN, FDB_DEV_BAD_INDEX, FDB_DEV_BAD_MASK = 1, 2, 4, 8
 STATIC_SCRATCH_BYTES = 8 << 20
-ABI_VERSION = 3
+ABI_VERSION = 4
 PREPARED_SCHEDULE, PREPARED_TABLES = 1, 2  # fdb_attn_params.prepared
 TUNE_ONE_LAUNCH, TUNE_TWO_LAUNCHES = 1, 2  # fdb_attn_params.tune
 
@@ -49,6 +49,7 @@ EXPORTS = (
     "fdb_abi_version", "fdb_last_error", "fdb_status_string", "fdb_build_bucket_lut", "fdb_relative_index",
     "fdb_attn_workspace_bytes", "fdb_attn_fwd", "fdb_attn_fwd_static", "fdb_attn_fwd_check", "fdb_relative_index_matrix",
     "fdb_quantize_e4m3", "fdb_add_layernorm", "fdb_linear_gelu", "fdb_embed_layernorm",
+    "fdb_attn_bwd_probs", "fdb_attn_bwd_bucket_sums",
 )
 
 _lib = None
@@ -102,6 +103,9 @@ def load() -> C.CDLL:
     lib.fdb_linear_gelu.restype = C.c_int
     lib.fdb_linear_gelu.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                     C.c_void_p, C.c_void_p]
+    for name in ("fdb_attn_bwd_probs", "fdb_attn_bwd_bucket_sums"):  # (const fdb_bwd_block*, stream); struct in backward.py
+        getattr(lib, name).restype = C.c_int
+        getattr(lib, name).argtypes = [C.c_void_p, C.c_void_p]
     if lib.fdb_abi_version() != ABI_VERSION:
         raise RuntimeError(f"libfdb_b200.so has ABI {lib.fdb_abi_version()}, this package expects {ABI_VERSION}: rebuild")
     _lib = lib

@@ -165,6 +165,64 @@ def bench_reference_triton(B: int, L: int, H: int, iters: int, warmup: int, nset
         "note": "reference = bias GEMMs (model.py:189-192) + flash_attention_with_disentangled; its (B,H,L,D) copies are not timed"}))
 
 
+def bench_backward(B: int, L: int, H: int, iters: int, warmup: int, with_reference: bool):
+    """Forward + backward of the attention op (gradients of q, k, v and both position tables), and the same through the
+    reference's autograd function (its bias GEMMs included, so that the table gradients exist there too) when asked."""
+    dev = torch.device("cuda")
+    D = 64
+    g = torch.Generator(device="cpu").manual_seed(0)
+    q, k, v, do = (torch.randn(B, L, H, D, generator=g).bfloat16().to(dev) for _ in range(4))
+    pk, pq = (torch.randn(H, 512, D, generator=g).mul_(0.5).bfloat16().to(dev) for _ in range(2))
+    kw = dict(max_seqlen=L, position_buckets=256, max_relative_positions=512)
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, pk, pq)]
+
+    def ours(i):
+        out = ops.disentangled_attention(*leaves, **kw)
+        return torch.autograd.grad(out, leaves, do)
+
+    def ours_fwd(i):
+        with torch.no_grad():
+            return ops.disentangled_attention(q, k, v, pk, pq, **kw)
+
+    g_ours = ours(0)
+    ms = _time(ours, iters, warmup)
+    ms_f = _time(ours_fwd, iters, warmup)
+    ops.check_status()
+    f = attn_flops([L] * B, H)
+    line = {"op": "attention_fwd_bwd", "batch": B, "seq": L, "heads": H, "fwd_bwd_ms_median": ms[0],
+            "fwd_ms_median": ms_f[0], "bwd_ms": ms[0] - ms_f[0],
+            "bwd_tflops_at_2.5x_fwd_flops": 2.5 * f / max(ms[0] - ms_f[0], 1e-9) / 1e9}
+    if with_reference:
+        ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+        if ref_root not in sys.path:
+            sys.path.insert(0, ref_root)
+        try:
+            from flashdeberta.ops.flash_attention import flash_attention_with_disentangled
+            sm_scale = 1.0 / (3 * D) ** 0.5
+            rl = [t.detach().clone().requires_grad_(True) for t in
+                  (q.permute(0, 2, 1, 3).contiguous(), k.permute(0, 2, 1, 3).contiguous(), v.permute(0, 2, 1, 3).contiguous(), pk, pq)]
+            dot = do.permute(0, 2, 1, 3).contiguous()
+
+            def theirs(i):
+                c2p = torch.matmul(rl[0], rl[3].unsqueeze(0).transpose(-1, -2))
+                p2c = torch.matmul(rl[1], rl[4].unsqueeze(0).transpose(-1, -2))
+                out = flash_attention_with_disentangled(rl[0], rl[1], rl[2], c2p, p2c, False, sm_scale, 256, 512)
+                return torch.autograd.grad(out, rl, dot)
+
+            g_ref = theirs(0)
+            ms_r = _time(theirs, iters, warmup)
+            line["reference_fwd_bwd_ms_median"] = ms_r[0]
+            line["speedup_fwd_bwd"] = ms_r[0] / ms[0]
+            for name, a, b in zip(("dq", "dk", "dv"), g_ours[:3], g_ref[:3]):
+                b = b.permute(0, 2, 1, 3)
+                line["rel_diff_" + name] = ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
+            for name, a, b in zip(("dpos_key", "dpos_query"), g_ours[3:], g_ref[3:]):
+                line["rel_diff_" + name] = ((a.float() - b.float()).abs().max() / b.float().abs().max()).item()
+        except Exception as e:  # the copy is not part of this repository's history; its Triton code may not compile here
+            line["reference_unavailable"] = repr(e)[:300]
+    print(json.dumps(line))
+
+
 def bench_eager_gpu(B: int, L: int, H: int, iters: int, warmup: int):
     """transformers' eager DisentangledSelfAttention module (the reference's fallback class, src/flashdeberta/model.py:255)
     on the GPU in fp32 and bf16, beside this package's module with the same weights; whole module, projections included."""
@@ -252,12 +310,15 @@ def main():
                     help="time transformers' eager attention module on the GPU (fp32, bf16) beside this package's module")
     ap.add_argument("--reference-triton", action="store_true",
                     help="time the reference's bias GEMMs + Triton kernel beside the fused call on the same inputs")
+    ap.add_argument("--backward", action="store_true", help="time forward + backward of the attention op")
     ap.add_argument("--out-features", type=int, default=3072)
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--hidden", type=int, default=768)
     args = ap.parse_args()
     if args.eager_gpu:
         return bench_eager_gpu(args.batch, args.seq, args.heads, args.iters, args.warmup)
+    if args.backward:
+        return bench_backward(args.batch, args.seq, args.heads, args.iters, args.warmup, args.reference_triton)
     if args.reference_triton:
         return bench_reference_triton(args.batch, args.seq, args.heads, args.iters, args.warmup, args.sets)
     if args.linear_gelu:

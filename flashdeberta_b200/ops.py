@@ -213,6 +213,13 @@ def disentangled_attention(
     D = q.shape[-1]
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D * (1 + int(pos_key is not None) + int(pos_query is not None)))
+    if wants_grad(q, k, v, pos_key, pos_query):
+        # autograd is recording: the call goes through the custom op, whose backward is flashdeberta_b200.backward
+        if scales is not None or return_lse:
+            raise RuntimeError("no gradient is implemented for the e4m3 path or for the LSE output; "
+                               "call under torch.no_grad() or detach the inputs")
+        return attn_fwd_op(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, int(max_seqlen), float(sm_scale),
+                           int(position_buckets), int(max_relative_positions))
     out = _out_like(q, torch.bfloat16)
     rows = out.numel() // (out.shape[-1] * out.shape[-2])
     lse = torch.empty(rows, q.shape[-2], dtype=torch.float32, device=q.device) if return_lse else None
@@ -275,6 +282,8 @@ def disentangled_attention_fp8(
     and per head for the position tables, the fused kernel runs its MMAs in e4m3 with fp32 accumulation (P is stored as
     2^8 * exp2(.) in e4m3), and the scales are folded back into the softmax scale and the output.  No counterpart in the
     reference.  Returns bf16."""
+    if wants_grad(q, k, v, pos_key, pos_query):
+        raise RuntimeError("the e4m3 attention is forward-only; train with attn_fp8 off")
     if q.dim() == 4:
         B, L = q.shape[0], q.shape[1]
         slabs = torch.arange(0, (B + 1) * L, L, dtype=torch.int32, device=q.device)
@@ -515,8 +524,50 @@ def _(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, p
     return torch.empty(q.shape, dtype=torch.bfloat16, device=q.device)
 
 
-def _no_backward(ctx, grad):
-    raise RuntimeError("flashdeberta_b200::attn_fwd is forward-only (inference); no backward is implemented")
+@torch.library.custom_op("flashdeberta_b200::attn_bwd", mutates_args=())
+def attn_bwd_op(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: Optional[torch.Tensor],
+                pos_query: Optional[torch.Tensor], cu_seqlens: Optional[torch.Tensor], seq_lens: Optional[torch.Tensor],
+                max_seqlen: int, sm_scale: float, position_buckets: int,
+                max_relative_positions: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gradients of ``attn_fwd`` (dq, dk, dv, dpos_key, dpos_query; an absent table gives an empty tensor).  The output
+    and the LSE are not kept from the forward: the fused forward is run again here, which costs a tenth of the backward
+    and keeps nothing but the inputs alive between the two."""
+    from . import backward
+    out, lse = disentangled_attention(q, k, v, pos_key, pos_query, cu_seqlens=cu_seqlens, seq_lens=seq_lens,
+                                      max_seqlen=max_seqlen, sm_scale=sm_scale, position_buckets=position_buckets,
+                                      max_relative_positions=max_relative_positions, return_lse=True)
+    dq, dk, dv, dpk, dpq = backward.attention_backward(
+        dout, q, k, v, pos_key, pos_query, out, lse, cu_seqlens=cu_seqlens, seq_lens=seq_lens, max_seqlen=max_seqlen,
+        sm_scale=sm_scale, position_buckets=position_buckets, max_relative_positions=max_relative_positions,
+        status=_status_word(q.device))
+    none = q.new_zeros(0)
+    return dq, dk, dv, none if dpk is None else dpk, none if dpq is None else dpq
 
 
-attn_fwd_op.register_autograd(_no_backward)
+@attn_bwd_op.register_fake
+def _(dout, q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
+      max_relative_positions):
+    none = q.new_zeros(0)
+    return (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v),
+            none if pos_key is None else torch.empty_like(pos_key), none if pos_query is None else torch.empty_like(pos_query))
+
+
+def _attn_setup(ctx, inputs, output):
+    q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets, max_rel = inputs
+    ctx.save_for_backward(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens)
+    ctx.fdb_args = (max_seqlen, sm_scale, position_buckets, max_rel)
+
+
+def _attn_backward(ctx, grad):
+    q, k, v, pos_key, pos_query, cu_seqlens, seq_lens = ctx.saved_tensors
+    dq, dk, dv, dpk, dpq = attn_bwd_op(grad.contiguous(), q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, *ctx.fdb_args)
+    return (dq, dk, dv, None if pos_key is None else dpk, None if pos_query is None else dpq,
+            None, None, None, None, None, None)
+
+
+attn_fwd_op.register_autograd(_attn_backward, setup_context=_attn_setup)
+
+
+def wants_grad(*tensors) -> bool:
+    """True when autograd is recording and one of the tensors takes part in it."""
+    return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)

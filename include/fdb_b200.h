@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define FDB_ABI_VERSION 3
+#define FDB_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define FDB_API __attribute__((visibility("default")))
@@ -207,6 +207,50 @@ FDB_API int fdb_attn_fwd(const fdb_attn_params* p, void* stream);
  */
 #define FDB_STATIC_SCRATCH_BYTES (8u << 20)
 FDB_API int fdb_attn_fwd_static(const fdb_attn_params* p, void* stream);
+
+/*
+ * Backward pass, the two steps that are not plain GEMMs.  The reference's backward is three Triton kernels
+ * (src/flashdeberta/ops/flash_attention.py:581-614 preprocess, :616-797 dK / dV with the position-bias gradients
+ * scattered by atomics at :770-786, :799-940 dQ, launcher :942-1030).  Here the host walks a group of sequences in
+ * blocks of query rows; the contractions (Q.K^T, dO.V^T, Q.pos_key^T, K.pos_query^T and every product with P or dS)
+ * are the caller's GEMMs, and the two entry points below do what lies between them.  All tensors contiguous, on the
+ * device; "group" = (sequence, head), sequence = group / heads; a block holds rows [row0, row0 + rows) of every group.
+ */
+typedef struct fdb_bwd_block {
+  uint32_t struct_bytes;       /* sizeof(fdb_bwd_block) */
+  int32_t groups;              /* sequences x heads (at most 65535) */
+  int32_t heads;
+  int32_t seqlen;              /* padded length: keys per group, row pitch of the score-shaped tensors */
+  int32_t row0, rows;          /* the block's query rows */
+  int32_t table_rows;          /* 2*att_span rows of the position tables; 0 = no position terms */
+  int32_t lut_d_min, lut_len;  /* bucket table as in fdb_attn_params */
+  float sm_scale;
+  const int32_t* seq_lens;     /* (sequences) valid lengths, right padding; NULL = every sequence full */
+  const int16_t* lut;
+  const int32_t* bucket_range; /* (table_rows, 2): first and last distance (inclusive) that address each table row;
+                                  INT32_MIN / INT32_MAX at the open ends; first > last for a row no distance addresses */
+  const float* scores;         /* (groups, rows, seqlen)  Q.K^T, unscaled */
+  const float* dprobs;         /* (groups, rows, seqlen)  dO.V^T */
+  const float* c2p;            /* (groups, rows, table_rows)  Q.pos_key^T, or NULL */
+  const float* p2c;            /* (groups, seqlen, table_rows)  K.pos_query^T, or NULL */
+  const float* lse;            /* (groups, rows) natural-log LSE of the forward */
+  const float* delta;          /* (groups, rows) sum over the head dimension of dO * O */
+  void* probs;                 /* out, bf16 (groups, rows, seqlen): P; zero outside the valid lengths */
+  void* dscores;               /* bf16 (groups, rows, seqlen): sm_scale * P * (dP - delta); written by fdb_attn_bwd_probs,
+                                  read by fdb_attn_bwd_bucket_sums */
+  float* c2p_sums;             /* out (groups, rows, table_rows): per query row, dscores summed over the keys that
+                                  address each table row; or NULL */
+  float* p2c_sums;             /* in/out (groups, seqlen, table_rows): per key, the same over this block's query rows,
+                                  ADDED to what is there (zero it before the first block); or NULL */
+  int32_t* status;             /* reserved (may be NULL) */
+} fdb_bwd_block;
+
+/* P = exp(sm_scale * (scores + c2p[m][idx(m-n)] + p2c[n][idx(m-n)]) - lse) and dscores of one block. */
+FDB_API int fdb_attn_bwd_probs(const fdb_bwd_block* p, void* stream);
+/* c2p_sums and / or p2c_sums of one block from its dscores (whichever pointers are set).  No global atomics: the index is
+ * non-decreasing in the distance, so the scores that share a table row are one run of keys (of query rows).
+ * table_rows at most 1598. */
+FDB_API int fdb_attn_bwd_bucket_sums(const fdb_bwd_block* p, void* stream);
 
 /*
  * Check kernel: the same contract computed with fp32 arithmetic on CUDA cores, one warp per (row, head), no

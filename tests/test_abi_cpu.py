@@ -45,6 +45,42 @@ def test_struct_layout_matches_the_header(tmp_path):
         assert int(out[f]) == getattr(_lib.AttnParams, f).offset, f
 
 
+def test_backward_block_layout_matches_the_header(tmp_path):
+    from flashdeberta_b200 import backward
+    fields = [f[0] for f in backward.BwdBlock._fields_]
+    src = tmp_path / "layout_bwd.c"
+    body = "\n".join(f'  printf("{f} %zu\\n", offsetof(fdb_bwd_block, {f}));' for f in fields)
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "fdb_b200.h"\nint main(void) {\n'
+        '  printf("sizeof %zu\\n", sizeof(fdb_bwd_block));\n' + body + "\n  return 0;\n}\n")
+    exe = tmp_path / "layout_bwd"
+    subprocess.check_call(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    out = dict(line.split() for line in subprocess.check_output([str(exe)], text=True).splitlines())
+    assert int(out["sizeof"]) == C.sizeof(backward.BwdBlock)
+    for f in fields:
+        assert int(out[f]) == getattr(backward.BwdBlock, f).offset, f
+
+
+def test_backward_block_argument_errors():
+    from flashdeberta_b200 import backward
+    lib = _lib.load()
+    p = backward.BwdBlock()
+    assert lib.fdb_attn_bwd_probs(C.byref(p), None) == -1          # struct_bytes missing
+    p.struct_bytes = C.sizeof(backward.BwdBlock)
+    p.groups, p.heads, p.seqlen, p.row0, p.rows = 6, 4, 128, 0, 64  # groups not a multiple of heads
+    assert lib.fdb_attn_bwd_probs(C.byref(p), None) == -1
+    p.groups = 8
+    p.row0 = 100                                                     # block reaches past the sequence
+    assert lib.fdb_attn_bwd_probs(C.byref(p), None) == -1
+    p.row0 = 0
+    assert lib.fdb_attn_bwd_probs(C.byref(p), None) == -1          # tensors missing
+    assert lib.fdb_attn_bwd_bucket_sums(C.byref(p), None) == -1    # no tables, no dscores
+    assert lib.fdb_last_error().decode() != ""
+    p.rows = 0
+    p.scores = p.dprobs = p.lse = p.delta = p.probs = p.dscores = 0x1000
+    assert lib.fdb_attn_bwd_probs(C.byref(p), None) == 0           # an empty block is a no-op
+
+
 def _configs(g):
     for k in g:
         if k.startswith("idx_"):
