@@ -17,50 +17,20 @@ With  s[m,n] = scale * (q_m.k_n + q_m.pk[i(m-n)] + k_n.pq[i(m-n)]),  p = exp(s -
   dQ_m = sum_n g[m,n] k_n + sum_b GC[m,b] pk_b           dK_n = sum_m g[m,n] q_m + sum_b GP[n,b] pq_b
   dpk_b = sum_m GC[m,b] q_m                              dpq_b = sum_n GP[n,b] k_n
 
-Memory: four (sequences x heads x block rows x keys) buffers at a time, the block sized to ``block_bytes``.
+Memory: four (sequences x heads x block rows x keys) buffers at a time (two fp32, two bf16), the block sized to
+``block_bytes`` (2 GiB by default: the per-block costs — the fp32 accumulations of dK and dV, the write-back of the p2c
+sums — shrink with the number of blocks).
 """
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, List, Optional, Tuple
+from typing import Optional, Tuple
 
-import numpy as np
 import torch
 
 from . import _lib, bucket
 
-_range_cache: Dict[Tuple[int, int, str], torch.Tensor] = {}
 _launches = 0  # kernels of this package launched by the functions below
-
-
-def bucket_ranges(position_buckets: int, max_relative_positions: int) -> np.ndarray:
-    """(2*att_span, 2) int32: the first and the last relative distance (inclusive) that address each row of the position
-    tables; the open ends are INT32_MIN / INT32_MAX, a row no distance addresses has first > last.  The index is
-    non-decreasing in the distance, so every row's distances are one interval."""
-    tab, d_min = bucket.host_lut(position_buckets, max_relative_positions)
-    rows = 2 * bucket.att_span(position_buckets, max_relative_positions)
-    rng = np.empty((rows, 2), dtype=np.int64)
-    rng[:, 0], rng[:, 1] = 1, 0
-    idx = tab.astype(np.int64)
-    if np.any(np.diff(idx) < 0):
-        raise RuntimeError("bucket table is not monotone")
-    d = d_min + np.arange(idx.size, dtype=np.int64)
-    first = np.full(rows, np.iinfo(np.int64).max)
-    last = np.full(rows, np.iinfo(np.int64).min)
-    np.minimum.at(first, idx, d)
-    np.maximum.at(last, idx, d)
-    hit = first <= last
-    rng[hit, 0], rng[hit, 1] = first[hit], last[hit]
-    rng[idx[0], 0] = np.iinfo(np.int32).min   # every distance below the table's first
-    rng[idx[-1], 1] = np.iinfo(np.int32).max  # and above its last
-    return rng.astype(np.int32)
-
-
-def _device_ranges(position_buckets: int, max_relative_positions: int, device: torch.device) -> torch.Tensor:
-    key = (int(position_buckets), int(max_relative_positions), str(device))
-    if key not in _range_cache:
-        _range_cache[key] = torch.from_numpy(bucket_ranges(position_buckets, max_relative_positions)).to(device)
-    return _range_cache[key]
 
 
 class BwdBlock(C.Structure):
@@ -70,7 +40,7 @@ class BwdBlock(C.Structure):
         ("struct_bytes", C.c_uint32), ("groups", C.c_int32), ("heads", C.c_int32), ("seqlen", C.c_int32),
         ("row0", C.c_int32), ("rows", C.c_int32), ("table_rows", C.c_int32), ("lut_d_min", C.c_int32),
         ("lut_len", C.c_int32), ("sm_scale", C.c_float),
-        ("seq_lens", C.c_void_p), ("lut", C.c_void_p), ("bucket_range", C.c_void_p),
+        ("seq_lens", C.c_void_p), ("lut", C.c_void_p),
         ("scores", C.c_void_p), ("dprobs", C.c_void_p), ("c2p", C.c_void_p), ("p2c", C.c_void_p),
         ("lse", C.c_void_p), ("delta", C.c_void_p), ("probs", C.c_void_p), ("dscores", C.c_void_p),
         ("c2p_sums", C.c_void_p), ("p2c_sums", C.c_void_p), ("status", C.c_void_p),
@@ -128,7 +98,7 @@ def _block_struct(blk: dict) -> BwdBlock:
     p.struct_bytes = C.sizeof(BwdBlock)
     p.groups, p.heads, p.seqlen, p.row0, p.rows = blk["groups"], blk["heads"], blk["seqlen"], blk["row0"], blk["rows"]
     p.table_rows, p.lut_d_min, p.lut_len, p.sm_scale = blk["table_rows"], blk["lut_d_min"], blk["lut_len"], blk["sm_scale"]
-    p.seq_lens, p.lut, p.bucket_range, p.status = _ptr(blk["seq_lens"]), _ptr(blk["lut"]), _ptr(blk["bucket_range"]), _ptr(blk["status"])
+    p.seq_lens, p.lut, p.status = _ptr(blk["seq_lens"]), _ptr(blk["lut"]), _ptr(blk["status"])
     return p
 
 
@@ -157,14 +127,13 @@ def _backward_block(q, k, v, o, do, lse, pos_key, pos_query, n_seq, seqlen, seq_
     delta = delta.view(n_seq, seqlen, H).permute(0, 2, 1).reshape(G, seqlen).contiguous()
     lse_h = lse.view(n_seq, seqlen, H).permute(0, 2, 1).reshape(G, seqlen).contiguous()
     has_c2p, has_p2c = pos_key is not None, pos_query is not None
-    blk = dict(groups=G, heads=H, seqlen=seqlen, table_rows=0, lut=None, lut_d_min=0, lut_len=0, bucket_range=None,
+    blk = dict(groups=G, heads=H, seqlen=seqlen, table_rows=0, lut=None, lut_d_min=0, lut_len=0,
                sm_scale=float(sm_scale), seq_lens=seq_lens, status=status, c2p=None, p2c=None)
     pkh = pqh = p2c_sums = None
     if has_c2p or has_p2c:
         lut, d_min = bucket.device_lut(position_buckets, max_relative_positions, dev)
         W = 2 * bucket.att_span(position_buckets, max_relative_positions)
-        blk.update(table_rows=W, lut=lut, lut_d_min=d_min, lut_len=lut.numel(),
-                   bucket_range=_device_ranges(position_buckets, max_relative_positions, dev))
+        blk.update(table_rows=W, lut=lut, lut_d_min=d_min, lut_len=lut.numel())
         if has_c2p:
             pkh = pos_key.to(torch.bfloat16).unsqueeze(0).expand(n_seq, H, W, D).reshape(G, W, D)
         if has_p2c:
@@ -211,7 +180,7 @@ def attention_backward(
     dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     pos_key: Optional[torch.Tensor], pos_query: Optional[torch.Tensor], out: torch.Tensor, lse: torch.Tensor,
     *, cu_seqlens: Optional[torch.Tensor] = None, seq_lens: Optional[torch.Tensor] = None, max_seqlen: int,
-    sm_scale: float, position_buckets: int = -1, max_relative_positions: int = -1, block_bytes: int = 1 << 29,
+    sm_scale: float, position_buckets: int = -1, max_relative_positions: int = -1, block_bytes: int = 1 << 31,
     status: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Gradients of ``ops.disentangled_attention`` for the bf16 path.  ``out`` and ``lse`` are what the forward returned

@@ -13,8 +13,6 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include <climits>
-
 #include "internal.h"
 
 namespace fdb {
@@ -32,16 +30,17 @@ __device__ __forceinline__ int seq_len_of(const fdb_bwd_block& a, int group) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// 1. P and dS of a block.  One CTA per (32 query rows x 64 keys) tile of one group.  The c2p term of a score sits in
+// 1. P and dS of a block.  One CTA per (32 query rows x 128 keys) tile of one group.  The c2p term of a score sits in
 // the row of its query, the p2c term in the row of its key, and consecutive keys (queries) address consecutive table
 // entries; so the tile is walked twice, once with a warp along the keys (coalesced reads of the scores and of the c2p
 // row) and once with a warp along the queries (coalesced reads of the p2c row), with the tile in shared memory between.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kPm = 32, kPn = 64, kPThreads = 256;
+constexpr int kPm = 32, kPn = 128, kPThreads = 256;
 
 __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
   __shared__ float s_s[kPm][kPn + 1];
   __shared__ float s_d[kPm][kPn + 1];
+  __shared__ int16_t s_idx[kPm + kPn];  // table row of every distance of the tile: entry (m - n) - d_lo
   const int g = blockIdx.z;
   const int r0 = blockIdx.y * kPm;   // first row of the tile inside the block
   const int n0 = blockIdx.x * kPn;
@@ -49,6 +48,11 @@ __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
   const int len = seq_len_of(a, g);
   const int64_t gl = (int64_t)g * a.rows;
   const bool pos = a.table_rows > 0 && a.lut != nullptr;
+  const int d_lo = a.row0 + r0 - (n0 + kPn - 1);
+  if (pos) {
+    if (threadIdx.x < kPm + kPn - 1) s_idx[threadIdx.x] = (int16_t)lut_at(a.lut, a.lut_d_min, a.lut_len, d_lo + (int)threadIdx.x);
+    __syncthreads();
+  }
 
   // pass 1, a warp along the keys: scores + c2p, and dP - delta
 #pragma unroll
@@ -63,7 +67,7 @@ __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
         const int64_t e = (gl + r) * a.seqlen + n;
         s = a.scores[e];
         d = a.dprobs[e] - a.delta[gl + r];
-        if (pos && a.c2p != nullptr) s += a.c2p[(gl + r) * a.table_rows + lut_at(a.lut, a.lut_d_min, a.lut_len, m - n)];
+        if (pos && a.c2p != nullptr) s += a.c2p[(gl + r) * a.table_rows + s_idx[m - n - d_lo]];
       }
       s_s[warp + 8 * i][lane + 32 * j] = s;
       s_d[warp + 8 * i][lane + 32 * j] = d;
@@ -83,7 +87,7 @@ __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
       if (r < a.rows && n < a.seqlen && m < len && n < len) {
         float s = s_s[lane][c];
         if (pos && a.p2c != nullptr)
-          s += a.p2c[((int64_t)g * a.seqlen + n) * a.table_rows + lut_at(a.lut, a.lut_d_min, a.lut_len, m - n)];
+          s += a.p2c[((int64_t)g * a.seqlen + n) * a.table_rows + s_idx[m - n - d_lo]];
         p = __expf(a.sm_scale * s - lse);
         ds = a.sm_scale * p * s_d[lane][c];
       }
@@ -111,62 +115,71 @@ __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// 2a. c2p sums: GC[m][b] = sum of dS[m][n] over the keys n with idx(m - n) == b, i.e. n in [m - last_b, m - first_b].
-// One CTA per (query row, group); thread b walks its own run of keys (short everywhere but at the two saturated ends,
-// whose runs the whole CTA sums together afterwards).
+// 2a. c2p sums: GC[m][b] = sum of dS[m][n] over the keys n with idx(m - n) == b.  Along a row the index never
+// increases, so the keys that share a table row are one run, and its sum is a difference of two running sums of the
+// row.  A CTA takes a few query rows in turn, 2048 keys at a time: every thread adds up its own eight consecutive keys,
+// a scan over the threads turns that into the running sum S(n) of the row, and a key n that ends a run (the next key
+// addresses another table row) adds +S(n) to its own table entry and -S(n) to the entry of the run that follows, in
+// a shared-memory row of table entries.  Two shared-memory atomics per run, none per key, and no global atomics.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int kCThreads = 256;
-constexpr int kLongRun = 64;
+constexpr int kCRows = 4;
+constexpr int kCPer = 8;  // consecutive keys per thread
 
 __global__ void __launch_bounds__(kCThreads) bwd_c2p_sums_kernel(fdb_bwd_block a) {
-  __shared__ float red[kCThreads / 32];
-  __shared__ int long_rows[8];
-  __shared__ int n_long;
-  const int r = blockIdx.x, g = blockIdx.y;
-  const int m = a.row0 + r;
+  extern __shared__ float acc_c[];  // [table_rows]
+  __shared__ float warp_tot[kCThreads / 32];
+  __shared__ float carry_s;
+  const int g = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int len = seq_len_of(a, g);
-  const int64_t row = (int64_t)g * a.rows + r;
-  const __nv_bfloat16* ds = static_cast<const __nv_bfloat16*>(a.dscores) + row * a.seqlen;
-  float* out = a.c2p_sums + row * a.table_rows;
-  if (threadIdx.x == 0) n_long = 0;
-  __syncthreads();
-  const int keys = m < len ? len : 0;  // rows of the padding have no keys
-  for (int b = threadIdx.x; b < a.table_rows; b += kCThreads) {
-    const int first = a.bucket_range[2 * b], last = a.bucket_range[2 * b + 1];
-    // n = m - d, d in [first, last]  ->  n in [m - last, m - first]; computed in 64 bits (the open ends are INT_MIN/MAX)
-    int64_t lo = (int64_t)m - last, hi = (int64_t)m - first;
-    lo = lo < 0 ? 0 : lo;
-    hi = hi > keys - 1 ? keys - 1 : hi;
-    float acc = 0.f;
-    if (first <= last && lo <= hi) {
-      if (hi - lo >= kLongRun) {
-        const int slot = atomicAdd(&n_long, 1);
-        if (slot < 8) long_rows[slot] = b;
-        else for (int64_t n = lo; n <= hi; ++n) acc += __bfloat162float(ds[n]);  // cannot happen with two open ends
-      } else {
-        for (int64_t n = lo; n <= hi; ++n) acc += __bfloat162float(ds[n]);
-      }
-    }
-    out[b] = acc;
-  }
-  __syncthreads();
-  const int todo = n_long < 8 ? n_long : 8;
-  for (int t = 0; t < todo; ++t) {
-    const int b = long_rows[t];
-    const int first = a.bucket_range[2 * b], last = a.bucket_range[2 * b + 1];
-    int64_t lo = (int64_t)m - last, hi = (int64_t)m - first;
-    lo = lo < 0 ? 0 : lo;
-    hi = hi > keys - 1 ? keys - 1 : hi;
-    float acc = 0.f;
-    for (int64_t n = lo + threadIdx.x; n <= hi; n += kCThreads) acc += __bfloat162float(ds[n]);
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  for (int rr = 0; rr < kCRows; ++rr) {
+    const int r = blockIdx.x * kCRows + rr;
+    if (r >= a.rows) break;  // the same for every thread
+    const int m = a.row0 + r;
+    const int64_t row = (int64_t)g * a.rows + r;
+    const __nv_bfloat16* ds = static_cast<const __nv_bfloat16*>(a.dscores) + row * a.seqlen;
+    for (int b = threadIdx.x; b < a.table_rows; b += kCThreads) acc_c[b] = 0.f;
+    if (threadIdx.x == 0) carry_s = 0.f;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      float s = 0.f;
-      for (int w = 0; w < kCThreads / 32; ++w) s += red[w];
-      out[b] = s;
+    const int keys = m < len ? len : 0;  // rows of the padding have no keys
+    for (int base = 0; base < keys; base += kCPer * kCThreads) {
+      const int n_first = base + (int)threadIdx.x * kCPer;
+      float v[kCPer];
+      int ix[kCPer + 1];  // table rows of my keys and of the key after them
+#pragma unroll
+      for (int u = 0; u < kCPer; ++u) v[u] = n_first + u < keys ? __bfloat162float(ds[n_first + u]) : 0.f;
+#pragma unroll
+      for (int u = 0; u <= kCPer; ++u) ix[u] = lut_at(a.lut, a.lut_d_min, a.lut_len, m - (n_first + u));
+      float run = 0.f;
+#pragma unroll
+      for (int u = 0; u < kCPer; ++u) { run += v[u]; v[u] = run; }  // running sum inside my keys
+      // exclusive scan of the threads' totals: inside the warp, then over the warps
+      float inc = run;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += up;
+      }
+      if (lane == 31) warp_tot[warp] = inc;
+      __syncthreads();
+      float before = carry_s + inc - run;
+      for (int w = 0; w < warp; ++w) before += warp_tot[w];
+#pragma unroll
+      for (int u = 0; u < kCPer; ++u) {
+        const int n = n_first + u;
+        if (n < keys && (n == keys - 1 || ix[u + 1] != ix[u])) {  // key n ends a run
+          const float upto = before + v[u];
+          atomicAdd(&acc_c[ix[u]], upto);
+          if (n < keys - 1) atomicAdd(&acc_c[ix[u + 1]], -upto);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == kCThreads - 1) carry_s = before + run;  // running sum at the end of these 2048 keys
+      __syncthreads();
     }
+    float* out = a.c2p_sums + row * a.table_rows;
+    for (int b = threadIdx.x; b < a.table_rows; b += kCThreads) out[b] = acc_c[b];
     __syncthreads();
   }
 }
@@ -178,39 +191,53 @@ __global__ void __launch_bounds__(kCThreads) bwd_c2p_sums_kernel(fdb_bwd_block a
 // hand-over goes to shared memory (one row of table entries per key), which is added to the global sums at the end,
 // only over the entries this block can have touched.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kQKeys = 32, kQThreads = 256;
+constexpr int kQKeys = 32, kQThreads = 256, kQSlices = kQThreads / 32;
 
 __global__ void __launch_bounds__(kQThreads) bwd_p2c_sums_kernel(fdb_bwd_block a) {
-  extern __shared__ float acc_s[];  // [kQKeys][pitch]
+  extern __shared__ float acc_s[];  // [kQKeys][pitch], then the table rows of the block's distances (int16)
   const int pitch = a.table_rows + 2;  // keys next to each other address entries next to each other: keep them in different banks
+  int16_t* idx_s = reinterpret_cast<int16_t*>(acc_s + kQKeys * pitch);
   const int g = blockIdx.y;
   const int n0 = blockIdx.x * kQKeys;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int len = seq_len_of(a, g);
-  // table entries this block can touch: distances (row0 - n0 - 31) .. (row0 + rows - 1 - n0)
-  const int b_lo = lut_at(a.lut, a.lut_d_min, a.lut_len, a.row0 - n0 - (kQKeys - 1));
-  const int b_hi = lut_at(a.lut, a.lut_d_min, a.lut_len, a.row0 + a.rows - 1 - n0);
+  // distances of this CTA: (row0 - n0 - 31) .. (row0 + rows - 1 - n0); idx_s[d - d_lo] is the table row of d
+  const int d_lo = a.row0 - n0 - (kQKeys - 1);
+  const int n_d = a.rows + kQKeys - 1;
+  for (int i = threadIdx.x; i < n_d; i += kQThreads) idx_s[i] = (int16_t)lut_at(a.lut, a.lut_d_min, a.lut_len, d_lo + i);
+  __syncthreads();
+  const int b_lo = idx_s[0], b_hi = idx_s[n_d - 1];  // the index never decreases with the distance
   const int span = b_hi - b_lo + 1;
   for (int i = threadIdx.x; i < kQKeys * span; i += kQThreads) acc_s[(i / span) * pitch + b_lo + i % span] = 0.f;
   __syncthreads();
   const int n = n0 + lane;
   if (n < len) {
-    const int per = (a.rows + 7) / 8;
+    const int per = (a.rows + kQSlices - 1) / kQSlices;
     const int r_begin = warp * per;
     int r_end = r_begin + per;
     r_end = r_end > a.rows ? a.rows : r_end;
     if (a.row0 + r_end > len) r_end = len - a.row0;  // rows of the padding carry zeros anyway
     const __nv_bfloat16* ds = static_cast<const __nv_bfloat16*>(a.dscores) + (int64_t)g * a.rows * a.seqlen + n;
+    const int16_t* my_idx = idx_s + (a.row0 - n - d_lo);  // my_idx[r] = table row of (row0 + r) - n
     int cur = -1;
     float acc = 0.f;
-    for (int r = r_begin; r < r_end; ++r) {
-      const int b = lut_at(a.lut, a.lut_d_min, a.lut_len, a.row0 + r - n);
-      if (b != cur) {
-        if (cur >= 0) atomicAdd(&acc_s[lane * pitch + cur], acc);
-        cur = b;
-        acc = 0.f;
+    for (int r = r_begin; r < r_end; r += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)  // eight loads in flight: the walk is bound by their latency otherwise
+        v[u] = r + u < r_end ? __bfloat162float(ds[(int64_t)(r + u) * a.seqlen]) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (r + u < r_end) {
+          const int b = my_idx[r + u];
+          if (b != cur) {
+            if (cur >= 0) atomicAdd(&acc_s[lane * pitch + cur], acc);
+            cur = b;
+            acc = 0.f;
+          }
+          acc += v[u];
+        }
       }
-      acc += __bfloat162float(ds[(int64_t)r * a.seqlen]);
     }
     if (cur >= 0) atomicAdd(&acc_s[lane * pitch + cur], acc);
   }
@@ -265,16 +292,19 @@ extern "C" FDB_API int fdb_attn_bwd_bucket_sums(const fdb_bwd_block* p, void* st
   clear_error();
   int rc = check_block(p);
   if (rc != FDB_OK) return rc;
-  if (p->dscores == nullptr || p->table_rows <= 0 || p->bucket_range == nullptr)
-    return fail(FDB_ERR_INVALID_ARGUMENT, "fdb_attn_bwd_bucket_sums: dscores, the bucket table and its ranges are required");
+  if (p->dscores == nullptr || p->table_rows <= 0)
+    return fail(FDB_ERR_INVALID_ARGUMENT, "fdb_attn_bwd_bucket_sums: dscores and the bucket table are required");
   if (p->groups == 0 || p->rows == 0 || p->seqlen == 0) return FDB_OK;
   if (p->c2p_sums != nullptr) {
-    bwd_c2p_sums_kernel<<<dim3(p->rows, p->groups), kCThreads, 0, static_cast<cudaStream_t>(stream)>>>(*p);
+    if (p->table_rows > 8192) return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: position tables of more than 8192 rows");
+    bwd_c2p_sums_kernel<<<dim3((p->rows + kCRows - 1) / kCRows, p->groups), kCThreads, sizeof(float) * p->table_rows,
+                          static_cast<cudaStream_t>(stream)>>>(*p);
     if ((rc = after_launch("bwd_c2p_sums_kernel")) != FDB_OK) return rc;
   }
   if (p->p2c_sums != nullptr) {
-    const size_t smem = sizeof(float) * kQKeys * (size_t)(p->table_rows + 2);
-    if (smem > 200 * 1024) return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: position tables of more than 1598 rows");
+    const size_t smem = sizeof(float) * kQKeys * (size_t)(p->table_rows + 2) + sizeof(int16_t) * ((size_t)p->rows + kQKeys);
+    if (smem > 200 * 1024)
+      return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: 128 * (table_rows + 2) + 2 * (rows + 32) bytes of shared memory exceed 200 KB");
     if (smem > 48 * 1024) {  // per device and cheap, so asked for on every such launch
       const cudaError_t e = cudaFuncSetAttribute(bwd_p2c_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "cudaFuncSetAttribute(bwd_p2c_sums_kernel): %s", cudaGetErrorString(e));

@@ -540,16 +540,15 @@ def attn_bwd_op(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
         dout, q, k, v, pos_key, pos_query, out, lse, cu_seqlens=cu_seqlens, seq_lens=seq_lens, max_seqlen=max_seqlen,
         sm_scale=sm_scale, position_buckets=position_buckets, max_relative_positions=max_relative_positions,
         status=_status_word(q.device))
-    none = q.new_zeros(0)
-    return dq, dk, dv, none if dpk is None else dpk, none if dpq is None else dpq
+    return dq, dk, dv, q.new_zeros(0) if dpk is None else dpk, q.new_zeros(0) if dpq is None else dpq
 
 
 @attn_bwd_op.register_fake
 def _(dout, q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
       max_relative_positions):
-    none = q.new_zeros(0)
     return (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v),
-            none if pos_key is None else torch.empty_like(pos_key), none if pos_query is None else torch.empty_like(pos_query))
+            q.new_zeros(0) if pos_key is None else torch.empty_like(pos_key),
+            q.new_zeros(0) if pos_query is None else torch.empty_like(pos_query))
 
 
 def _attn_setup(ctx, inputs, output):

@@ -227,8 +227,6 @@ typedef struct fdb_bwd_block {
   float sm_scale;
   const int32_t* seq_lens;     /* (sequences) valid lengths, right padding; NULL = every sequence full */
   const int16_t* lut;
-  const int32_t* bucket_range; /* (table_rows, 2): first and last distance (inclusive) that address each table row;
-                                  INT32_MIN / INT32_MAX at the open ends; first > last for a row no distance addresses */
   const float* scores;         /* (groups, rows, seqlen)  Q.K^T, unscaled */
   const float* dprobs;         /* (groups, rows, seqlen)  dO.V^T */
   const float* c2p;            /* (groups, rows, table_rows)  Q.pos_key^T, or NULL */
@@ -249,7 +247,8 @@ typedef struct fdb_bwd_block {
 FDB_API int fdb_attn_bwd_probs(const fdb_bwd_block* p, void* stream);
 /* c2p_sums and / or p2c_sums of one block from its dscores (whichever pointers are set).  No global atomics: the index is
  * non-decreasing in the distance, so the scores that share a table row are one run of keys (of query rows).
- * table_rows at most 1598. */
+ * table_rows at most 8192;
+ * 128 * (table_rows + 2) + 2 * (rows + 32) bytes of shared memory, at most 200 KB (FDB_ERR_LIMIT). */
 FDB_API int fdb_attn_bwd_bucket_sums(const fdb_bwd_block* p, void* stream);
 
 /*

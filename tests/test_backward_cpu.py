@@ -2,7 +2,6 @@
 the table-row intervals, with the two CUDA stages replaced by a few lines of torch that do what their contract says.
 The reference gradients come from autograd through the fp32 oracle.  (The CUDA stages themselves are checked on the GPU
 in tests/test_backward_gpu.py.)"""
-import numpy as np
 import pytest
 import torch
 
@@ -112,13 +111,3 @@ def test_packed_sequences_match_autograd(fake_stages):
                                       sm_scale=sm, position_buckets=buckets, max_relative_positions=max_rel)
     for name, a, b in zip(("dq", "dk", "dv", "dpos_key", "dpos_query"), got, want):
         _close(a, b, name)
-
-
-def test_bucket_ranges_partition_the_distances():
-    for buckets, max_rel in [(256, 512), (32, 64), (-1, 40)]:
-        rng = backward.bucket_ranges(buckets, max_rel).astype(np.int64)
-        rows = 2 * bucket.att_span(buckets, max_rel)
-        assert rng.shape == (rows, 2)
-        for d in list(range(-1500, 1500, 7)) + [-40000, 40000]:
-            hit = np.nonzero((rng[:, 0] <= d) & (d <= rng[:, 1]))[0]
-            assert hit.tolist() == [bucket.relative_index(d, buckets, max_rel)], d
