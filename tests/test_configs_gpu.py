@@ -232,11 +232,13 @@ def test_custom_op_direct_traced_and_opcheck():
         assert fo.shape == q.shape and fo.dtype == torch.bfloat16
     torch.library.opcheck(torch.ops.flashdeberta_b200.attn_fwd.default, (q, k, v, pk, pq, None, lens, L, sm, 256, 512),
                           test_utils=("test_schema", "test_faketensor"))
-    # forward only: asking for a gradient raises (as the reference's packed op does, flash_attention_varlen.py:481-483)
+    # the op records a backward (tests/test_backward_gpu.py holds it to the oracle's autograd); opcheck on its registration
     qg = q.clone().requires_grad_(True)
     o = torch.ops.flashdeberta_b200.attn_fwd(qg, k, v, pk, pq, None, lens, L, sm, 256, 512)
-    with pytest.raises(RuntimeError, match="forward-only"):
-        o.float().sum().backward()
+    o.float().sum().backward()
+    assert qg.grad is not None and torch.isfinite(qg.grad.float()).all() and qg.grad[1, 170:].abs().max().item() == 0
+    torch.library.opcheck(torch.ops.flashdeberta_b200.attn_fwd.default, (qg.detach().requires_grad_(True), k, v, pk, pq, None, lens, L, sm, 256, 512),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
     # the module traced as one graph: the attention is the custom-op node
     hs = torch.randn(B, L, 256, generator=g).bfloat16().to(DEV)
     rel = (torch.randn(512, 256, generator=g) * 0.02).bfloat16().to(DEV)
