@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
               for (int c = 0; c < 16; ++c) {
                 const int cc = 16 * hf + c;
                 const uint32_t x = (lane + cc <= 30) ? t1[c] : t0[c];
-                const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - cc) & 31);
+                const uint32_t y = __shfl_sync(0xffffffffu, x, lane + 31 - cc);  // the source lane is taken modulo 32
                 s[32 * ch + cc] = fmaf(__uint_as_float(y), ratio_p, __uint_as_float(a[cc]));
               }
             }
@@ -539,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_fwd_kernel(const __grid_cons
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
               const uint32_t x = (lane + c <= 30) ? t1[c] : t0[c];
-              const uint32_t y = __shfl_sync(0xffffffffu, x, (lane + 31 - c) & 31);
+              const uint32_t y = __shfl_sync(0xffffffffu, x, lane + 31 - c);  // the source lane is taken modulo 32
               s[32 * ch + c] = fmaf(__uint_as_float(y), ratio_p, __uint_as_float(a[c]));
             }
           }
