@@ -54,6 +54,66 @@ __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
     __syncthreads();
   }
 
+  // A tile that lies inside the block, inside the sequence and on an even row pitch takes the short way: no bounds
+  // checks, two keys per global access.
+  if (r0 + kPm <= a.rows && n0 + kPn <= len && a.row0 + r0 + kPm <= len && (a.seqlen & 1) == 0) {
+    const bool has_c2p = pos && a.c2p != nullptr, has_p2c = pos && a.p2c != nullptr;
+#pragma unroll
+    for (int i = 0; i < kPm / 8; ++i) {
+      const int rl = warp + 8 * i;
+      const int64_t row = gl + r0 + rl;
+      const float2* sp = reinterpret_cast<const float2*>(a.scores + row * a.seqlen + n0);
+      const float2* dp = reinterpret_cast<const float2*>(a.dprobs + row * a.seqlen + n0);
+      const float* cp = has_c2p ? a.c2p + row * a.table_rows : nullptr;
+      const float delta = a.delta[row];
+      const int16_t* ix = s_idx + (rl + kPn - 1);  // ix[-c] = table row of (row - key c of the tile)
+#pragma unroll
+      for (int j = 0; j < kPn / 64; ++j) {
+        const int c = 2 * lane + 64 * j;
+        float2 sv = sp[lane + 32 * j];
+        const float2 dv = dp[lane + 32 * j];
+        if (has_c2p) {
+          sv.x += cp[ix[-c]];
+          sv.y += cp[ix[-c - 1]];
+        }
+        s_s[rl][c] = sv.x;
+        s_s[rl][c + 1] = sv.y;
+        s_d[rl][c] = dv.x - delta;
+        s_d[rl][c + 1] = dv.y - delta;
+      }
+    }
+    __syncthreads();
+    {
+      const float lse = a.lse[gl + r0 + lane];
+      const int16_t* ix = s_idx + (lane + kPn - 1);
+      const float* pp = has_p2c ? a.p2c + ((int64_t)g * a.seqlen + n0) * a.table_rows : nullptr;
+#pragma unroll
+      for (int j = 0; j < kPn / 8; ++j) {
+        const int c = warp + 8 * j;
+        float sc = s_s[lane][c];
+        if (has_p2c) sc += pp[(int64_t)c * a.table_rows + ix[-c]];
+        const float pr = __expf(a.sm_scale * sc - lse);
+        s_s[lane][c] = pr;
+        s_d[lane][c] = a.sm_scale * pr * s_d[lane][c];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < kPm / 8; ++i) {
+      const int rl = warp + 8 * i;
+      const int64_t row = gl + r0 + rl;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(a.probs) + row * a.seqlen + n0);
+      __nv_bfloat162* go = reinterpret_cast<__nv_bfloat162*>(static_cast<__nv_bfloat16*>(a.dscores) + row * a.seqlen + n0);
+#pragma unroll
+      for (int j = 0; j < kPn / 64; ++j) {
+        const int c = 2 * lane + 64 * j;
+        po[lane + 32 * j] = __floats2bfloat162_rn(s_s[rl][c], s_s[rl][c + 1]);
+        go[lane + 32 * j] = __floats2bfloat162_rn(s_d[rl][c], s_d[rl][c + 1]);
+      }
+    }
+    return;
+  }
+
   // pass 1, a warp along the keys: scores + c2p, and dP - delta
 #pragma unroll
   for (int i = 0; i < kPm / 8; ++i) {
@@ -185,13 +245,13 @@ __global__ void __launch_bounds__(kCThreads) bwd_c2p_sums_kernel(fdb_bwd_block a
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// 2b. p2c sums: GP[n][b] += sum of dS[m][n] over the block's query rows m with idx(m - n) == b.  One CTA per (32 keys,
-// group): lane = key (coalesced reads of dS), the eight warps take an eighth of the block's rows each.  Walking down a
+// 2b. p2c sums: GP[n][b] += sum of dS[m][n] over the block's query rows m with idx(m - n) == b.  One CTA per (16 keys,
+// group): half a warp along the keys (32-byte reads of dS), sixteen slices of the block's rows per CTA.  Walking down a
 // column the index never decreases, so a thread keeps a running sum and hands it over when the index changes; the
 // hand-over goes to shared memory (one row of table entries per key), which is added to the global sums at the end,
 // only over the entries this block can have touched.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kQKeys = 32, kQThreads = 256, kQSlices = kQThreads / 32;
+constexpr int kQKeys = 16, kQThreads = 256, kQSlices = kQThreads / kQKeys;
 
 __global__ void __launch_bounds__(kQThreads) bwd_p2c_sums_kernel(fdb_bwd_block a) {
   extern __shared__ float acc_s[];  // [kQKeys][pitch], then the table rows of the block's distances (int16)
@@ -210,10 +270,12 @@ __global__ void __launch_bounds__(kQThreads) bwd_p2c_sums_kernel(fdb_bwd_block a
   const int span = b_hi - b_lo + 1;
   for (int i = threadIdx.x; i < kQKeys * span; i += kQThreads) acc_s[(i / span) * pitch + b_lo + i % span] = 0.f;
   __syncthreads();
-  const int n = n0 + lane;
+  const int key = lane & (kQKeys - 1);         // half a warp along the keys (32-byte reads of dS) ...
+  const int slice = 2 * warp + (lane >> 4);    // ... and sixteen slices of the block's rows per CTA
+  const int n = n0 + key;
   if (n < len) {
     const int per = (a.rows + kQSlices - 1) / kQSlices;
-    const int r_begin = warp * per;
+    const int r_begin = slice * per;
     int r_end = r_begin + per;
     r_end = r_end > a.rows ? a.rows : r_end;
     if (a.row0 + r_end > len) r_end = len - a.row0;  // rows of the padding carry zeros anyway
@@ -231,7 +293,7 @@ __global__ void __launch_bounds__(kQThreads) bwd_p2c_sums_kernel(fdb_bwd_block a
         if (r + u < r_end) {
           const int b = my_idx[r + u];
           if (b != cur) {
-            if (cur >= 0) atomicAdd(&acc_s[lane * pitch + cur], acc);
+            if (cur >= 0) atomicAdd(&acc_s[key * pitch + cur], acc);
             cur = b;
             acc = 0.f;
           }
@@ -239,13 +301,13 @@ __global__ void __launch_bounds__(kQThreads) bwd_p2c_sums_kernel(fdb_bwd_block a
         }
       }
     }
-    if (cur >= 0) atomicAdd(&acc_s[lane * pitch + cur], acc);
+    if (cur >= 0) atomicAdd(&acc_s[key * pitch + cur], acc);
   }
   __syncthreads();
   float* out = a.p2c_sums + ((int64_t)g * a.seqlen + n0) * a.table_rows;
   for (int i = threadIdx.x; i < kQKeys * span; i += kQThreads) {
-    const int key = i / span, b = b_lo + i % span;
-    if (n0 + key < len) out[(int64_t)key * a.table_rows + b] += acc_s[key * pitch + b];
+    const int k2 = i / span, b = b_lo + i % span;
+    if (n0 + k2 < len) out[(int64_t)k2 * a.table_rows + b] += acc_s[k2 * pitch + b];
   }
 }
 
@@ -304,7 +366,7 @@ extern "C" FDB_API int fdb_attn_bwd_bucket_sums(const fdb_bwd_block* p, void* st
   if (p->p2c_sums != nullptr) {
     const size_t smem = sizeof(float) * kQKeys * (size_t)(p->table_rows + 2) + sizeof(int16_t) * ((size_t)p->rows + kQKeys);
     if (smem > 200 * 1024)
-      return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: 128 * (table_rows + 2) + 2 * (rows + 32) bytes of shared memory exceed 200 KB");
+      return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: 64 * (table_rows + 2) + 2 * (rows + 16) bytes of shared memory exceed 200 KB");
     if (smem > 48 * 1024) {  // per device and cheap, so asked for on every such launch
       const cudaError_t e = cudaFuncSetAttribute(bwd_p2c_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "cudaFuncSetAttribute(bwd_p2c_sums_kernel): %s", cudaGetErrorString(e));

@@ -248,7 +248,7 @@ FDB_API int fdb_attn_bwd_probs(const fdb_bwd_block* p, void* stream);
 /* c2p_sums and / or p2c_sums of one block from its dscores (whichever pointers are set).  No global atomics: the index is
  * non-decreasing in the distance, so the scores that share a table row are one run of keys (of query rows).
  * table_rows at most 8192;
- * 128 * (table_rows + 2) + 2 * (rows + 32) bytes of shared memory, at most 200 KB (FDB_ERR_LIMIT). */
+ * 64 * (table_rows + 2) + 2 * (rows + 16) bytes of shared memory, at most 200 KB (FDB_ERR_LIMIT). */
 FDB_API int fdb_attn_bwd_bucket_sums(const fdb_bwd_block* p, void* stream);
 
 /*
