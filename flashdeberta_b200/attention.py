@@ -176,8 +176,8 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
             if self.attn_fp8:
                 out = ops.disentangled_attention_fp8(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query, **kw)
             elif ops.wants_grad(q, k, v, pos_key, pos_query):  # training: the op with a backward
-                out = ops.attn_fwd_op(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query, pk.cu_seqlens,
-                                      None, pk.max_seqlen, sm_scale, buckets, max_rel)
+                out = ops.attn_fwd_train_op(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query,
+                                            pk.cu_seqlens, None, pk.max_seqlen, sm_scale, buckets, max_rel)[0]
             else:
                 out = ops.disentangled_attention(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query,
                                                  prepared=self._prepared, **kw)
@@ -188,7 +188,9 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
             out = ops.disentangled_attention_fp8(q, k, v, pos_key, pos_query, seq_lens=seq_lens, max_seqlen=L,
                                                  sm_scale=sm_scale, position_buckets=buckets,
                                                  max_relative_positions=max_rel)
-        elif torch.compiler.is_compiling() or ops.wants_grad(q, k, v, pos_key, pos_query):
+        elif ops.wants_grad(q, k, v, pos_key, pos_query):  # training: output and LSE kept for the backward
+            out = ops.attn_fwd_train_op(q, k, v, pos_key, pos_query, None, seq_lens, L, sm_scale, buckets, max_rel)[0]
+        elif torch.compiler.is_compiling():
             out = ops.attn_fwd_op(q, k, v, pos_key, pos_query, None, seq_lens, L, sm_scale, buckets, max_rel)
         else:
             out = ops.disentangled_attention(q, k, v, pos_key, pos_query, seq_lens=seq_lens, max_seqlen=L,

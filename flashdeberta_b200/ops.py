@@ -214,12 +214,13 @@ def disentangled_attention(
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(D * (1 + int(pos_key is not None) + int(pos_query is not None)))
     if wants_grad(q, k, v, pos_key, pos_query):
-        # autograd is recording: the call goes through the custom op, whose backward is flashdeberta_b200.backward
+        # autograd is recording: the call goes through the training op (output and LSE kept), whose backward is
+        # flashdeberta_b200.backward
         if scales is not None or return_lse:
             raise RuntimeError("no gradient is implemented for the e4m3 path or for the LSE output; "
                                "call under torch.no_grad() or detach the inputs")
-        return attn_fwd_op(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, int(max_seqlen), float(sm_scale),
-                           int(position_buckets), int(max_relative_positions))
+        return attn_fwd_train_op(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, int(max_seqlen), float(sm_scale),
+                                 int(position_buckets), int(max_relative_positions))[0]
     out = _out_like(q, torch.bfloat16)
     rows = out.numel() // (out.shape[-1] * out.shape[-2])
     lse = torch.empty(rows, q.shape[-2], dtype=torch.float32, device=q.device) if return_lse else None
@@ -526,16 +527,18 @@ def _(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, p
 
 @torch.library.custom_op("flashdeberta_b200::attn_bwd", mutates_args=())
 def attn_bwd_op(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: Optional[torch.Tensor],
-                pos_query: Optional[torch.Tensor], cu_seqlens: Optional[torch.Tensor], seq_lens: Optional[torch.Tensor],
-                max_seqlen: int, sm_scale: float, position_buckets: int,
+                pos_query: Optional[torch.Tensor], out: Optional[torch.Tensor], lse: Optional[torch.Tensor],
+                cu_seqlens: Optional[torch.Tensor], seq_lens: Optional[torch.Tensor], max_seqlen: int, sm_scale: float,
+                position_buckets: int,
                 max_relative_positions: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Gradients of ``attn_fwd`` (dq, dk, dv, dpos_key, dpos_query; an absent table gives an empty tensor).  The output
-    and the LSE are not kept from the forward: the fused forward is run again here, which costs a tenth of the backward
-    and keeps nothing but the inputs alive between the two."""
+    """Gradients of the attention (dq, dk, dv, dpos_key, dpos_query; an absent table gives an empty tensor).  ``out``
+    and ``lse`` are the forward's results when the caller kept them (``attn_fwd_train``); without them the fused forward
+    is run again here, which costs less than a tenth of the backward and keeps nothing but the inputs alive."""
     from . import backward
-    out, lse = disentangled_attention(q, k, v, pos_key, pos_query, cu_seqlens=cu_seqlens, seq_lens=seq_lens,
-                                      max_seqlen=max_seqlen, sm_scale=sm_scale, position_buckets=position_buckets,
-                                      max_relative_positions=max_relative_positions, return_lse=True)
+    if out is None or lse is None:
+        out, lse = disentangled_attention(q, k, v, pos_key, pos_query, cu_seqlens=cu_seqlens, seq_lens=seq_lens,
+                                          max_seqlen=max_seqlen, sm_scale=sm_scale, position_buckets=position_buckets,
+                                          max_relative_positions=max_relative_positions, return_lse=True)
     dq, dk, dv, dpk, dpq = backward.attention_backward(
         dout, q, k, v, pos_key, pos_query, out, lse, cu_seqlens=cu_seqlens, seq_lens=seq_lens, max_seqlen=max_seqlen,
         sm_scale=sm_scale, position_buckets=position_buckets, max_relative_positions=max_relative_positions,
@@ -544,7 +547,7 @@ def attn_bwd_op(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.T
 
 
 @attn_bwd_op.register_fake
-def _(dout, q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
+def _(dout, q, k, v, pos_key, pos_query, out, lse, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
       max_relative_positions):
     return (torch.empty_like(q), torch.empty_like(k), torch.empty_like(v),
             q.new_zeros(0) if pos_key is None else torch.empty_like(pos_key),
@@ -559,12 +562,52 @@ def _attn_setup(ctx, inputs, output):
 
 def _attn_backward(ctx, grad):
     q, k, v, pos_key, pos_query, cu_seqlens, seq_lens = ctx.saved_tensors
-    dq, dk, dv, dpk, dpq = attn_bwd_op(grad.contiguous(), q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, *ctx.fdb_args)
+    dq, dk, dv, dpk, dpq = attn_bwd_op(grad.contiguous(), q, k, v, pos_key, pos_query, None, None, cu_seqlens, seq_lens,
+                                       *ctx.fdb_args)
     return (dq, dk, dv, None if pos_key is None else dpk, None if pos_query is None else dpq,
             None, None, None, None, None, None)
 
 
 attn_fwd_op.register_autograd(_attn_backward, setup_context=_attn_setup)
+
+
+@torch.library.custom_op("flashdeberta_b200::attn_fwd_train", mutates_args=())
+def attn_fwd_train_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_key: Optional[torch.Tensor],
+                      pos_query: Optional[torch.Tensor], cu_seqlens: Optional[torch.Tensor],
+                      seq_lens: Optional[torch.Tensor], max_seqlen: int, sm_scale: float, position_buckets: int,
+                      max_relative_positions: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The forward as the training path calls it: returns the output and the natural-log LSE (rows, heads), both kept
+    for the backward so that it does not run the forward again.  The LSE output carries no gradient."""
+    return disentangled_attention(q, k, v, pos_key, pos_query, cu_seqlens=cu_seqlens, seq_lens=seq_lens,
+                                  max_seqlen=max_seqlen, sm_scale=sm_scale, position_buckets=position_buckets,
+                                  max_relative_positions=max_relative_positions, return_lse=True)
+
+
+@attn_fwd_train_op.register_fake
+def _(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets,
+      max_relative_positions):
+    rows = q.numel() // (q.shape[-1] * q.shape[-2])
+    return (torch.empty(q.shape, dtype=torch.bfloat16, device=q.device),
+            torch.empty(rows, q.shape[-2], dtype=torch.float32, device=q.device))
+
+
+def _train_setup(ctx, inputs, output):
+    q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, max_seqlen, sm_scale, position_buckets, max_rel = inputs
+    out, lse = output
+    ctx.save_for_backward(q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, out, lse)
+    ctx.fdb_args = (max_seqlen, sm_scale, position_buckets, max_rel)
+    ctx.mark_non_differentiable(lse)
+
+
+def _train_backward(ctx, grad, grad_lse):
+    q, k, v, pos_key, pos_query, cu_seqlens, seq_lens, out, lse = ctx.saved_tensors
+    dq, dk, dv, dpk, dpq = attn_bwd_op(grad.contiguous(), q, k, v, pos_key, pos_query, out, lse, cu_seqlens, seq_lens,
+                                       *ctx.fdb_args)
+    return (dq, dk, dv, None if pos_key is None else dpk, None if pos_query is None else dpq,
+            None, None, None, None, None, None)
+
+
+attn_fwd_train_op.register_autograd(_train_backward, setup_context=_train_setup)
 
 
 def wants_grad(*tensors) -> bool:
