@@ -73,13 +73,13 @@ def test_dense_ragged_gradients_vs_oracle_autograd(buckets, max_rel, c2p, p2c):
 
 
 def test_packed_gradients_in_several_blocks_vs_oracle_autograd():
-    """Packed sequences (one of a single token, one of 1500) with the row blocks forced small, so that the p2c sums are
+    """Packed sequences (an empty one, one of a single token, one of 1500) with the row blocks forced small, so that the p2c sums are
     accumulated over many blocks and the block edges fall inside the bucketed band."""
     from flashdeberta_b200 import backward, ops
     g = torch.Generator().manual_seed(22)
     H, D = 3, 64
-    lens = [1500, 1, 260]
-    cu = [0, 1500, 1501, 1761]
+    lens = [1500, 0, 1, 261]  # an empty sequence, a single token, an odd length
+    cu = [0, 1500, 1500, 1501, 1762]
     T = cu[-1]
     q, k, v, dout = (torch.randn(T, H, D, generator=g).bfloat16().to(DEV) for _ in range(4))
     pk, pq = (torch.randn(H, 512, D, generator=g).bfloat16().to(DEV) for _ in range(2))
