@@ -14,12 +14,15 @@ What differs inside:
 from __future__ import annotations
 
 import math
+import warnings
 from typing import Optional
 
 import torch
 from transformers.models.deberta_v2.modeling_deberta_v2 import DisentangledSelfAttention
 
 from . import _lib, ops
+
+_warned_general = False
 
 
 class PackedSequences:
@@ -137,6 +140,32 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
             self._pos_cache = (key, pos_key, pos_query, rel_embeddings)  # keep the table alive so id() stays unique
         return pos_key, pos_query
 
+    def _forward_general(self, q, k, v, pos_key, pos_query, attention_mask, sm_scale, buckets, max_rel, in_dtype):
+        """Head sizes other than 64 (up to 128; the reference's test has one such shape, tests/attention.py:87-89, no
+        DeBERTa checkpoint has): the library's general kernel, fp32 arithmetic on CUDA cores.  Correct and slow (it is the
+        kernel the fused one is validated with); forward only."""
+        B, L, H, D = q.shape
+        if D > 128:
+            raise ValueError(f"head size {D} is not supported (64 on the fused kernel, up to 128 on the general one)")
+        if ops.wants_grad(q, k, v, pos_key, pos_query) or self.attn_fp8:
+            raise RuntimeError("training and e4m3 attention need a head size of 64")
+        global _warned_general
+        if not _warned_general:
+            warnings.warn(f"flashdeberta_b200: head size {D} runs on the general CUDA-core kernel, far below the speed of the "
+                          "fused kernel (head size 64)")
+            _warned_general = True
+        if isinstance(attention_mask, PackedSequences):
+            pk = attention_mask
+            out = ops.disentangled_attention_check(q.view(L, H, D), k.view(L, H, D), v.view(L, H, D), pos_key, pos_query,
+                                                   cu_seqlens=pk.cu_seqlens, max_seqlen=pk.max_seqlen, sm_scale=sm_scale,
+                                                   position_buckets=buckets, max_relative_positions=max_rel)
+        else:
+            out = ops.disentangled_attention_check(q, k, v, pos_key, pos_query, seq_lens=lengths_from_mask(attention_mask),
+                                                   max_seqlen=L, sm_scale=sm_scale, position_buckets=buckets,
+                                                   max_relative_positions=max_rel)
+        out = out.reshape(B, L, H * D)
+        return (out if in_dtype == torch.bfloat16 else out.to(in_dtype), None)
+
     # -- forward -------------------------------------------------------------------------------------------------------------
     def forward(self, hidden_states, attention_mask, output_attentions=False, query_states=None, relative_pos=None,
                 rel_embeddings=None):
@@ -168,6 +197,8 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
 
         if in_dtype != torch.bfloat16:
             q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+        if D != 64:
+            return self._forward_general(q, k, v, pos_key, pos_query, attention_mask, sm_scale, buckets, max_rel, in_dtype)
         if isinstance(attention_mask, PackedSequences):
             # packed tokens: hidden_states is (1, T, hidden); every sequence is addressed through cu_seqlens
             pk = attention_mask

@@ -204,6 +204,33 @@ def test_module_query_states_vs_live_eager():
     _ops().check_status()
 
 
+def test_module_head_size_128_runs_on_the_general_kernel():
+    """Head size 128 (the one such shape in the reference's test, tests/attention.py:87-89): the module takes the library's
+    general kernel, dense and packed; training there is refused."""
+    import warnings
+    from flashdeberta_b200.attention import PackedSequences
+    eager, flash, g = _module_pair(256, 2)  # 256 / 2 heads = 128
+    B, L = 2, 260
+    hs = torch.randn(B, L, 256, generator=g).bfloat16().float().to(DEV)
+    rel = (torch.randn(512, 256, generator=g) * 0.02).bfloat16().float().to(DEV)
+    mask = torch.ones(B, L, device=DEV)
+    mask[1, 99:] = 0
+    with torch.no_grad(), warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        want = eager(hs, _ext(mask), rel_embeddings=rel)[0]
+        got = flash(hs.bfloat16(), mask, rel_embeddings=rel.bfloat16())[0]
+        packed = PackedSequences.from_mask(mask)
+        got_p = packed.unpack(flash(packed.pack(hs.bfloat16()), packed, rel_embeddings=rel.bfloat16())[0])
+    valid = mask.bool().unsqueeze(-1)
+    _close(got * valid, want * valid, BF16_MAX, BF16_MEAN, "head size 128, dense")
+    _close(got_p * valid, want * valid, BF16_MAX, BF16_MEAN, "head size 128, packed")
+    assert got[1, 99:].abs().max().item() == 0
+    with pytest.raises(RuntimeError, match="head size of 64"), warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        flash.train()(hs.bfloat16().requires_grad_(True), mask, rel_embeddings=rel.bfloat16())
+    _ops().check_status()
+
+
 def test_custom_op_direct_traced_and_opcheck():
     """flashdeberta_b200::attn_fwd, the torch-facing boundary: called directly, through the module under torch.compile
     (whole graph, fake tensors propagated through register_fake) and through torch.library.opcheck."""
