@@ -164,7 +164,7 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
                                                    max_seqlen=L, sm_scale=sm_scale, position_buckets=buckets,
                                                    max_relative_positions=max_rel)
         out = out.reshape(B, L, H * D)
-        return (out if in_dtype == torch.bfloat16 else out.to(in_dtype), None)
+        return (out if out.dtype == in_dtype else out.to(in_dtype), None)
 
     # -- forward -------------------------------------------------------------------------------------------------------------
     def forward(self, hidden_states, attention_mask, output_attentions=False, query_states=None, relative_pos=None,
@@ -192,13 +192,17 @@ class FlashDisentangledSelfAttention(DisentangledSelfAttention):
         if self.relative_attention and scale_factor > 1:
             if rel_embeddings is None:
                 raise ValueError("rel_embeddings is required when relative_attention is on")
-            pos_key, pos_query = self._position_tables(rel_embeddings, torch.bfloat16)
+            # the general kernel (head sizes other than 64) also computes in fp32 from fp32 inputs: no rounding at all
+            table_dtype = torch.float32 if (D != 64 and in_dtype == torch.float32) else torch.bfloat16
+            pos_key, pos_query = self._position_tables(rel_embeddings, table_dtype)
             buckets, max_rel = self.position_buckets, self.max_relative_positions
 
+        if D != 64:
+            if in_dtype not in (torch.float32, torch.bfloat16):
+                q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+            return self._forward_general(q, k, v, pos_key, pos_query, attention_mask, sm_scale, buckets, max_rel, in_dtype)
         if in_dtype != torch.bfloat16:
             q, k, v = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
-        if D != 64:
-            return self._forward_general(q, k, v, pos_key, pos_query, attention_mask, sm_scale, buckets, max_rel, in_dtype)
         if isinstance(attention_mask, PackedSequences):
             # packed tokens: hidden_states is (1, T, hidden); every sequence is addressed through cu_seqlens
             pk = attention_mask

@@ -231,6 +231,27 @@ def test_module_head_size_128_runs_on_the_general_kernel():
     _ops().check_status()
 
 
+def test_reference_suite_shape_in_fp32():
+    """The one case of the reference's own forward test (tests/attention.py:81-104): batch 1 x 2048 tokens, hidden 1024,
+    8 heads (head size 128), fp32 modules, all-ones mask, separate position projections; its bar is a mean absolute
+    difference below 1e-4 against transformers' module."""
+    import warnings
+    eager, flash, g = _module_pair(1024, 8, share=False)
+    flash = flash.float()
+    hs = torch.randn(1, 2048, 1024, generator=g).to(DEV)
+    rel = torch.randn(512, 1024, generator=g).to(DEV)
+    mask = torch.ones(1, 2048, device=DEV)
+    with torch.no_grad(), warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        want = eager(hs, _ext(mask), rel_embeddings=rel)[0]
+        got = flash(hs, mask, rel_embeddings=rel)[0]
+    assert got.dtype == torch.float32
+    diff = (got - want).abs()
+    assert diff.mean().item() < 1e-4, diff.mean().item()
+    assert diff.max().item() < 1e-3, diff.max().item()
+    _ops().check_status()
+
+
 def test_custom_op_direct_traced_and_opcheck():
     """flashdeberta_b200::attn_fwd, the torch-facing boundary: called directly, through the module under torch.compile
     (whole graph, fake tensors propagated through register_fake) and through torch.library.opcheck."""
