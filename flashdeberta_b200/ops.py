@@ -177,7 +177,11 @@ class PreparedWorkspace:
     it can be used again (``fdb_attn_params.prepared``): the position tables gathered through the bucket index as long
     as the same table tensors come back unmodified, the order of the query tiles as long as the batch has the same shape
     and either no padding or the same, unmodified lengths tensor.  Workspaces above ``max_bytes`` (long sequences in two launches: partial results per row) are not
-    kept; such calls take a fresh scratch buffer as without this object."""
+    kept; such calls take a fresh scratch buffer as without this object.
+
+    "Unmodified" is judged by the tensor's address and version counter.  A write that bypasses the counter (through
+    ``.data``, a DLPack alias, a raw CUDA kernel) is not seen: after such a write to a lengths or table tensor, pass a new
+    tensor or drop this object (``module._prepared = ops.PreparedWorkspace()``)."""
 
     max_bytes = 64 << 20
 
