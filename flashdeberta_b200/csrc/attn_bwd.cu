@@ -177,71 +177,79 @@ __global__ void __launch_bounds__(kPThreads) bwd_probs_kernel(fdb_bwd_block a) {
 // ---------------------------------------------------------------------------------------------------------------------
 // 2a. c2p sums: GC[m][b] = sum of dS[m][n] over the keys n with idx(m - n) == b.  Along a row the index never
 // increases, so the keys that share a table row are one run, and its sum is a difference of two running sums of the
-// row.  A CTA takes a few query rows in turn, 2048 keys at a time: every thread adds up its own eight consecutive keys,
-// a scan over the threads turns that into the running sum S(n) of the row, and a key n that ends a run (the next key
+// row.  A warp takes a query row, 256 keys at a time: every lane adds up its own eight consecutive keys (one 16-byte
+// load), a scan over the lanes turns that into the running sum S(n) of the row, and a key n that ends a run (the next key
 // addresses another table row) adds +S(n) to its own table entry and -S(n) to the entry of the run that follows, in
 // a shared-memory row of table entries.  Two shared-memory atomics per run, none per key, and no global atomics.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int kCThreads = 256;
-constexpr int kCRows = 4;
-constexpr int kCPer = 8;  // consecutive keys per thread
+constexpr int kCWarps = kCThreads / 32;  // query rows per CTA: a warp each
+constexpr int kCPer = 8;                 // consecutive keys per lane
 
 __global__ void __launch_bounds__(kCThreads) bwd_c2p_sums_kernel(fdb_bwd_block a) {
-  extern __shared__ float acc_c[];  // [table_rows]
-  __shared__ float warp_tot[kCThreads / 32];
-  __shared__ float carry_s;
+  extern __shared__ float acc_c[];  // [kCWarps][table_rows], then the bucket table (int16[lut_len])
+  int16_t* lut_s = reinterpret_cast<int16_t*>(acc_c + kCWarps * a.table_rows);
   const int g = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int len = seq_len_of(a, g);
-  for (int rr = 0; rr < kCRows; ++rr) {
-    const int r = blockIdx.x * kCRows + rr;
-    if (r >= a.rows) break;  // the same for every thread
-    const int m = a.row0 + r;
-    const int64_t row = (int64_t)g * a.rows + r;
-    const __nv_bfloat16* ds = static_cast<const __nv_bfloat16*>(a.dscores) + row * a.seqlen;
-    for (int b = threadIdx.x; b < a.table_rows; b += kCThreads) acc_c[b] = 0.f;
-    if (threadIdx.x == 0) carry_s = 0.f;
-    __syncthreads();
-    const int keys = m < len ? len : 0;  // rows of the padding have no keys
-    for (int base = 0; base < keys; base += kCPer * kCThreads) {
-      const int n_first = base + (int)threadIdx.x * kCPer;
-      float v[kCPer];
-      int ix[kCPer + 1];  // table rows of my keys and of the key after them
+  for (int i = threadIdx.x; i < a.lut_len; i += kCThreads) lut_s[i] = a.lut[i];
+  for (int i = threadIdx.x; i < kCWarps * a.table_rows; i += kCThreads) acc_c[i] = 0.f;
+  __syncthreads();
+  const int r = blockIdx.x * kCWarps + warp;
+  if (r >= a.rows) return;
+  const int m = a.row0 + r;
+  const int64_t row = (int64_t)g * a.rows + r;
+  const __nv_bfloat16* ds = static_cast<const __nv_bfloat16*>(a.dscores) + row * a.seqlen;
+  float* acc = acc_c + warp * a.table_rows;
+  const bool vec = ((row * a.seqlen) & 7) == 0;  // the row starts on a 16-byte boundary
+  const int keys = m < len ? len : 0;            // rows of the padding have no keys
+  float carry = 0.f;                             // running sum of the row in front of this chunk
+  for (int base = 0; base < keys; base += kCPer * 32) {
+    const int n_first = base + lane * kCPer;
+    float v[kCPer];
+    if (vec && n_first + kCPer <= keys) {
+      const uint4 w = *reinterpret_cast<const uint4*>(ds + n_first);
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[2 * u] = __uint_as_float(ww[u] << 16);
+        v[2 * u + 1] = __uint_as_float(ww[u] & 0xffff0000u);
+      }
+    } else {
 #pragma unroll
       for (int u = 0; u < kCPer; ++u) v[u] = n_first + u < keys ? __bfloat162float(ds[n_first + u]) : 0.f;
-#pragma unroll
-      for (int u = 0; u <= kCPer; ++u) ix[u] = lut_at(a.lut, a.lut_d_min, a.lut_len, m - (n_first + u));
-      float run = 0.f;
-#pragma unroll
-      for (int u = 0; u < kCPer; ++u) { run += v[u]; v[u] = run; }  // running sum inside my keys
-      // exclusive scan of the threads' totals: inside the warp, then over the warps
-      float inc = run;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, inc, o);
-        if (lane >= o) inc += up;
-      }
-      if (lane == 31) warp_tot[warp] = inc;
-      __syncthreads();
-      float before = carry_s + inc - run;
-      for (int w = 0; w < warp; ++w) before += warp_tot[w];
-#pragma unroll
-      for (int u = 0; u < kCPer; ++u) {
-        const int n = n_first + u;
-        if (n < keys && (n == keys - 1 || ix[u + 1] != ix[u])) {  // key n ends a run
-          const float upto = before + v[u];
-          atomicAdd(&acc_c[ix[u]], upto);
-          if (n < keys - 1) atomicAdd(&acc_c[ix[u + 1]], -upto);
-        }
-      }
-      __syncthreads();
-      if (threadIdx.x == kCThreads - 1) carry_s = before + run;  // running sum at the end of these 2048 keys
-      __syncthreads();
     }
-    float* out = a.c2p_sums + row * a.table_rows;
-    for (int b = threadIdx.x; b < a.table_rows; b += kCThreads) out[b] = acc_c[b];
-    __syncthreads();
+    int ix[kCPer + 1];  // table rows of my keys and of the key after them
+#pragma unroll
+    for (int u = 0; u <= kCPer; ++u) {
+      int i = m - (n_first + u) - a.lut_d_min;
+      i = i < 0 ? 0 : (i >= a.lut_len ? a.lut_len - 1 : i);
+      ix[u] = lut_s[i];
+    }
+    float run = 0.f;
+#pragma unroll
+    for (int u = 0; u < kCPer; ++u) { run += v[u]; v[u] = run; }  // running sum inside my keys
+    float inc = run;  // inclusive scan of the lanes' totals
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += up;
+    }
+    const float before = carry + inc - run;
+#pragma unroll
+    for (int u = 0; u < kCPer; ++u) {
+      const int n = n_first + u;
+      if (n < keys && (n == keys - 1 || ix[u + 1] != ix[u])) {  // key n ends a run
+        const float upto = before + v[u];
+        atomicAdd(&acc[ix[u]], upto);
+        if (n < keys - 1) atomicAdd(&acc[ix[u + 1]], -upto);
+      }
+    }
+    carry = __shfl_sync(0xffffffffu, before + run, 31);
   }
+  __syncwarp();
+  float* out = a.c2p_sums + row * a.table_rows;
+  for (int b = lane; b < a.table_rows; b += 32) out[b] = acc[b];
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -359,8 +367,13 @@ extern "C" FDB_API int fdb_attn_bwd_bucket_sums(const fdb_bwd_block* p, void* st
   if (p->groups == 0 || p->rows == 0 || p->seqlen == 0) return FDB_OK;
   if (p->c2p_sums != nullptr) {
     if (p->table_rows > 8192) return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: position tables of more than 8192 rows");
-    bwd_c2p_sums_kernel<<<dim3((p->rows + kCRows - 1) / kCRows, p->groups), kCThreads, sizeof(float) * p->table_rows,
-                          static_cast<cudaStream_t>(stream)>>>(*p);
+    const size_t smem_c = sizeof(float) * kCWarps * (size_t)p->table_rows + sizeof(int16_t) * (size_t)p->lut_len;
+    if (smem_c > 200 * 1024) return fail(FDB_ERR_LIMIT, "fdb_attn_bwd_bucket_sums: 32 * table_rows + 2 * lut_len bytes of shared memory exceed 200 KB");
+    if (smem_c > 48 * 1024) {
+      const cudaError_t e = cudaFuncSetAttribute(bwd_c2p_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_c);
+      if (e != cudaSuccess) return fail(FDB_ERR_CUDA, "cudaFuncSetAttribute(bwd_c2p_sums_kernel): %s", cudaGetErrorString(e));
+    }
+    bwd_c2p_sums_kernel<<<dim3((p->rows + kCWarps - 1) / kCWarps, p->groups), kCThreads, smem_c, static_cast<cudaStream_t>(stream)>>>(*p);
     if ((rc = after_launch("bwd_c2p_sums_kernel")) != FDB_OK) return rc;
   }
   if (p->p2c_sums != nullptr) {
